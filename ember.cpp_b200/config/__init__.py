@@ -4,6 +4,7 @@ from .base import (Architecture, ConfigError, ModelConfig, architectures, config
 from .gpt2 import GELU_FORMS, GPT2Config
 from .muzozen import MuzozenConfig
 from .nipolorn import NipolornConfig
+from .sosutar import SosutarConfig
 
-__all__ = ["Architecture", "ConfigError", "GELU_FORMS", "GPT2Config", "ModelConfig", "MuzozenConfig", "NipolornConfig", "architectures",
+__all__ = ["Architecture", "ConfigError", "GELU_FORMS", "GPT2Config", "ModelConfig", "MuzozenConfig", "NipolornConfig", "SosutarConfig", "architectures",
            "config_from_dict", "get_architecture", "load_config", "register_architecture"]

@@ -139,7 +139,8 @@ __global__ void __launch_bounds__(128)
 attention_plain_kernel(const T* __restrict__ qkv, const T* __restrict__ kc, const T* __restrict__ vc,
                        T* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ token_seq,
                        const int* __restrict__ seq_slot, const int* __restrict__ pages, int max_blocks, int T_tokens,
-                       int n_heads, int kv_heads, int hd, float scale, int window, int vd, int keep_first) {
+                       int n_heads, int kv_heads, int hd, float scale, int window, int vd, int keep_first,
+                       const float* __restrict__ slopes, const float* __restrict__ sinks) {
   __shared__ float q_s[4][kMaxHeadDim];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int item = blockIdx.x * 4 + warp;
@@ -160,7 +161,9 @@ attention_plain_kernel(const T* __restrict__ qkv, const T* __restrict__ kc, cons
   for (int d = lane; d < hd; d += 32) q_s[warp][d] = to_float(q[d]);
   __syncwarp();
 
-  float m = -INFINITY, l = 0.f;
+  // a sink is one more term of the softmax's denominator, exp(sink), with no key and no value
+  float m = sinks ? sinks[h] : -INFINITY, l = sinks ? 1.f : 0.f;
+  const float slope = slopes ? slopes[h] : 0.f;   // a score loses slope * (distance to the key)
   float acc[kMaxHeadDim / 32];
 #pragma unroll
   for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.f;
@@ -180,7 +183,7 @@ attention_plain_kernel(const T* __restrict__ qkv, const T* __restrict__ kc, cons
       const T* k = kc + row * hd;
       float dot = 0.f;
       for (int d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], to_float(k[d]), dot);
-      sc = dot * scale;
+      sc = dot * scale - slope * (float)(p - j);
     }
     const float m_new = fmaxf(m, warp_max(sc));
     const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
@@ -209,10 +212,18 @@ attention_plain_kernel(const T* __restrict__ qkv, const T* __restrict__ kc, cons
   }
 }
 
+EMBER_API int ember_attention_plain_biased(const void* qkv, const void* kc, const void* vc, void* out, const int* positions,
+                                           const int* token_seq, const int* seq_slot, const int* pages, int max_blocks, int T,
+                                           int n_heads, int kv_heads, int hd, float scale, int window, int vd, int keep_first,
+                                           const float* slopes, const float* sinks, int dtype, cudaStream_t stream);
+
 EMBER_API int ember_attention_plain_v(const void* qkv, const void* kc, const void* vc, void* out, const int* positions,
                                       const int* token_seq, const int* seq_slot, const int* pages, int max_blocks, int T,
                                       int n_heads, int kv_heads, int hd, float scale, int window, int vd, int keep_first,
-                                      int dtype, cudaStream_t stream);
+                                      int dtype, cudaStream_t stream) {
+  return ember_attention_plain_biased(qkv, kc, vc, out, positions, token_seq, seq_slot, pages, max_blocks, T, n_heads, kv_heads,
+                                      hd, scale, window, vd, keep_first, nullptr, nullptr, dtype, stream);
+}
 
 EMBER_API int ember_attention_plain(const void* qkv, const void* kc, const void* vc, void* out, const int* positions,
                                     const int* token_seq, const int* seq_slot, const int* pages, int max_blocks, int T,
@@ -223,11 +234,13 @@ EMBER_API int ember_attention_plain(const void* qkv, const void* kc, const void*
 }
 
 // The same with values of `vd` per head and the first `keep_first` positions of a sequence visible beside the
-// window: query p sees key j <= p if p - j < window or j < keep_first (window 0: all keys).
-EMBER_API int ember_attention_plain_v(const void* qkv, const void* kc, const void* vc, void* out, const int* positions,
-                                      const int* token_seq, const int* seq_slot, const int* pages, int max_blocks, int T,
-                                      int n_heads, int kv_heads, int hd, float scale, int window, int vd, int keep_first,
-                                      int dtype, cudaStream_t stream) {
+// window: query p sees key j <= p if p - j < window or j < keep_first (window 0: all keys).  slopes (float32 per
+// query head, or null): the score of key j loses slopes[h] * (p - j).  sinks (float32 per query head, or null): the
+// softmax's denominator also holds exp(sinks[h]).
+EMBER_API int ember_attention_plain_biased(const void* qkv, const void* kc, const void* vc, void* out, const int* positions,
+                                           const int* token_seq, const int* seq_slot, const int* pages, int max_blocks, int T,
+                                           int n_heads, int kv_heads, int hd, float scale, int window, int vd, int keep_first,
+                                           const float* slopes, const float* sinks, int dtype, cudaStream_t stream) {
   EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0, "attention: bad sizes");
   EMBER_CHECK(n_heads % kv_heads == 0, "attention: %d heads are not a multiple of %d key/value heads", n_heads,
               kv_heads);
@@ -239,11 +252,11 @@ EMBER_API int ember_attention_plain_v(const void* qkv, const void* kc, const voi
   if (dtype == EMBER_F32)
     attention_plain_kernel<float><<<grid, 128, 0, stream>>>((const float*)qkv, (const float*)kc, (const float*)vc,
                                                             (float*)out, positions, token_seq, seq_slot, pages,
-                                                            max_blocks, T, n_heads, kv_heads, hd, scale, window, vd, keep_first);
+                                                            max_blocks, T, n_heads, kv_heads, hd, scale, window, vd, keep_first, slopes, sinks);
   else if (dtype == EMBER_BF16)
     attention_plain_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
         (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, positions,
-        token_seq, seq_slot, pages, max_blocks, T, n_heads, kv_heads, hd, scale, window, vd, keep_first);
+        token_seq, seq_slot, pages, max_blocks, T, n_heads, kv_heads, hd, scale, window, vd, keep_first, slopes, sinks);
   else
     return ember_fail("attention: element type %d", dtype);
   EMBER_LAUNCH_OK("attention_plain");

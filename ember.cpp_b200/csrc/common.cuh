@@ -18,7 +18,7 @@
 enum : int { EMBER_F32 = 0, EMBER_BF16 = 1 };
 
 // activation codes of the linear epilogues
-enum : int { EMBER_ACT_NONE = 0, EMBER_ACT_GELU_TANH = 1, EMBER_ACT_GELU_ERF = 2 };
+enum : int { EMBER_ACT_NONE = 0, EMBER_ACT_GELU_TANH = 1, EMBER_ACT_GELU_ERF = 2, EMBER_ACT_RELU2 = 3 };  // 3: the square of relu
 
 constexpr int kPage = 64;  // positions per cache page
 
@@ -67,6 +67,7 @@ __device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + e
 __device__ __forceinline__ float apply_act(float v, int act) {
   if (act == EMBER_ACT_GELU_TANH) return gelu_tanh(v);
   if (act == EMBER_ACT_GELU_ERF) return gelu_erf(v);
+  if (act == EMBER_ACT_RELU2) return v > 0.f ? v * v : 0.f;
   return v;
 }
 

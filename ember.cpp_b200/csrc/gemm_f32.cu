@@ -64,7 +64,7 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, const 
 EMBER_API int ember_gemm_f32(const float* A, const float* W, const float* bias, const float* residual, float* out,
                              int M, int N, int K, int act, cudaStream_t stream) {
   EMBER_CHECK(M > 0 && N > 0 && K > 0, "gemm_f32: M = %d, N = %d, K = %d", M, N, K);
-  EMBER_CHECK(act >= 0 && act <= 2, "gemm_f32: activation %d", act);
+  EMBER_CHECK(act >= 0 && act <= 3, "gemm_f32: activation %d", act);
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   EMBER_CHECK(grid.y <= 65535, "gemm_f32: %d rows are more than one launch takes", M);
   gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, W, bias, residual, out, M, N, K, act);

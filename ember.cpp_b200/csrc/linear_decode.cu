@@ -337,7 +337,7 @@ EMBER_API int ember_linear_decode(const void* xin, const void* W, const float* b
                                   cudaStream_t stream) {
   EMBER_CHECK(M > 0 && M <= 16 && N > 0 && K > 0, "linear_decode: M = %d (at most 16), N = %d, K = %d", M, N, K);
   EMBER_CHECK(K % 8 == 0, "linear_decode: K = %d is not a multiple of 8 (16-byte rows)", K);
-  EMBER_CHECK(act >= 0 && act <= 2, "linear_decode: activation %d", act);
+  EMBER_CHECK(act >= 0 && act <= 3, "linear_decode: activation %d", act);
   EMBER_CHECK(out_dtype == EMBER_F32 || out_dtype == EMBER_BF16, "linear_decode: output type %d", out_dtype);
   EMBER_CHECK(!residual || out_dtype == EMBER_F32, "linear_decode: a residual sum needs a float32 output");
   EMBER_CHECK(warm_bytes % 16 == 0 && (reinterpret_cast<size_t>(warm) & 15) == 0,

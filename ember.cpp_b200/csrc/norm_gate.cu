@@ -158,14 +158,17 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
   }
 }
 
+__device__ __forceinline__ float gatef(float z, int kind) { return kind == 1 ? sigmoidf(z) : z * sigmoidf(z); }
+
 // out = unit(y * silu(z)) * w, the root mean square taken over each of `parts` equal pieces of a row.
 // y float32 [T, n]; z: n columns of a wider matrix (row stride z_stride).  grid (T, parts).
 // VEC: the part's width, the row widths and the gate's row stride are multiples of 4 (and the gate's first column too).
 // GATE_FIRST false: out = unit(y) * w * silu(z), the root mean square being y's own (the gate comes after the norm).
+// kind 1: the gate is sigmoid(z) in place of silu(z).
 template <typename T, bool VEC, bool GATE_FIRST>
 __global__ void __launch_bounds__(kThreads)
 gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, long long z_stride,
-                        const float* __restrict__ w, T* __restrict__ out, int n, int part, float eps) {
+                        const float* __restrict__ w, T* __restrict__ out, int n, int part, float eps, int kind) {
   __shared__ float red[kThreads / 32];
   const size_t t = blockIdx.x;
   const int c0 = blockIdx.y * part;
@@ -176,30 +179,30 @@ gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, lo
   if constexpr (VEC) {
     for (int i = threadIdx.x * 4; i < part; i += blockDim.x * 4) {
       const float4 a = load4(yr + i), g = load4(zr + i);
-      const float v0 = GATE_FIRST ? a.x * (g.x * sigmoidf(g.x)) : a.x, v1 = GATE_FIRST ? a.y * (g.y * sigmoidf(g.y)) : a.y,
-                  v2 = GATE_FIRST ? a.z * (g.z * sigmoidf(g.z)) : a.z, v3 = GATE_FIRST ? a.w * (g.w * sigmoidf(g.w)) : a.w;
+      const float v0 = GATE_FIRST ? a.x * gatef(g.x, kind) : a.x, v1 = GATE_FIRST ? a.y * gatef(g.y, kind) : a.y,
+                  v2 = GATE_FIRST ? a.z * gatef(g.z, kind) : a.z, v3 = GATE_FIRST ? a.w * gatef(g.w, kind) : a.w;
       ss = fmaf(v0, v0, fmaf(v1, v1, fmaf(v2, v2, fmaf(v3, v3, ss))));
     }
     const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)part + eps);
     for (int i = threadIdx.x * 4; i < part; i += blockDim.x * 4) {
       const float4 a = load4(yr + i), g = load4(zr + i), gain = load4(w + c0 + i);
       if constexpr (GATE_FIRST)
-        store4(o + i, a.x * (g.x * sigmoidf(g.x)) * inv * gain.x, a.y * (g.y * sigmoidf(g.y)) * inv * gain.y,
-               a.z * (g.z * sigmoidf(g.z)) * inv * gain.z, a.w * (g.w * sigmoidf(g.w)) * inv * gain.w);
+        store4(o + i, a.x * gatef(g.x, kind) * inv * gain.x, a.y * gatef(g.y, kind) * inv * gain.y,
+               a.z * gatef(g.z, kind) * inv * gain.z, a.w * gatef(g.w, kind) * inv * gain.w);
       else
-        store4(o + i, a.x * inv * gain.x * (g.x * sigmoidf(g.x)), a.y * inv * gain.y * (g.y * sigmoidf(g.y)),
-               a.z * inv * gain.z * (g.z * sigmoidf(g.z)), a.w * inv * gain.w * (g.w * sigmoidf(g.w)));
+        store4(o + i, a.x * inv * gain.x * gatef(g.x, kind), a.y * inv * gain.y * gatef(g.y, kind),
+               a.z * inv * gain.z * gatef(g.z, kind), a.w * inv * gain.w * gatef(g.w, kind));
     }
   } else {
     for (int i = threadIdx.x; i < part; i += blockDim.x) {
       const float zv = to_float(zr[i]);
-      const float v = GATE_FIRST ? yr[i] * (zv * sigmoidf(zv)) : yr[i];
+      const float v = GATE_FIRST ? yr[i] * gatef(zv, kind) : yr[i];
       ss = fmaf(v, v, ss);
     }
     const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)part + eps);
     for (int i = threadIdx.x; i < part; i += blockDim.x) {
       const float zv = to_float(zr[i]);
-      o[i] = from_float<T>(GATE_FIRST ? yr[i] * (zv * sigmoidf(zv)) * inv * w[c0 + i] : yr[i] * inv * w[c0 + i] * (zv * sigmoidf(zv)));
+      o[i] = from_float<T>(GATE_FIRST ? yr[i] * gatef(zv, kind) * inv * w[c0 + i] : yr[i] * inv * w[c0 + i] * gatef(zv, kind));
     }
   }
 }
@@ -270,6 +273,7 @@ EMBER_API int ember_gated_group_norm(const float* y, const void* z, long long z_
                                      int n, int parts, float eps, int gate_first, int dtype, cudaStream_t stream) {
   EMBER_CHECK(rows > 0 && n > 0 && parts > 0 && n % parts == 0, "gated_group_norm: %d rows of %d in %d parts", rows, n, parts);
   EMBER_CHECK(parts <= 65535, "gated_group_norm: %d parts exceed one launch", parts);
+  const int kind = (gate_first >> 1) & 1;   // bit 0: the gate before the norm; bit 1: a sigmoid gate in place of silu
   const dim3 grid(rows, parts);
   const int elem = dtype == EMBER_F32 ? 4 : 2;
   // a part as short as a head takes a warp or two, not a block of eight that mostly idle
@@ -280,8 +284,8 @@ EMBER_API int ember_gated_group_norm(const float* y, const void* z, long long z_
   cudaError_t e;
 #define EMBER_GGN1(T, VEC, FIRST)                                                                                  \
   launch_plain(gated_group_norm_kernel<T, VEC, FIRST>, grid, dim3(threads), 0, stream, y, (const T*)z, z_stride, w, (T*)out, \
-               n, n / parts, eps)
-#define EMBER_GGN(T, VEC) (gate_first ? EMBER_GGN1(T, VEC, true) : EMBER_GGN1(T, VEC, false))
+               n, n / parts, eps, kind)
+#define EMBER_GGN(T, VEC) ((gate_first & 1) ? EMBER_GGN1(T, VEC, true) : EMBER_GGN1(T, VEC, false))
   if (dtype == EMBER_F32)
     e = vec ? EMBER_GGN(float, true) : EMBER_GGN(float, false);
   else if (dtype == EMBER_BF16)

@@ -18,13 +18,14 @@ import torch
 from . import build
 
 _F32, _BF16 = 0, 1
-_ACT = {None: 0, "gelu_tanh": 1, "gelu_erf": 2}
+_ACT = {None: 0, "gelu_tanh": 1, "gelu_erf": 2, "relu2": 3}
 _LT_WORKSPACE = 32 << 20
 
 _c_int, _c_float, _c_void, _c_size, _c_u64 = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint64
 
 _SIGNATURES = {
-    "ember_embed": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_int, _c_void],
+    "ember_embed": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_int, _c_float,
+                    _c_void],
     "ember_layernorm": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ember_gather_rows": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_void],
     "ember_take_tokens": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
@@ -96,6 +97,17 @@ _SIGNATURES = {
     "ember_delta_rule": [_c_void, _c_void, ctypes.c_longlong, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void,
                          _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
                          _c_int, _c_void],
+    "ember_attention_plain_biased": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
+                                     _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void],
+    "ember_add_branches": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_float, _c_void],
+    "ember_qkv_norm": [_c_void, ctypes.c_longlong, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
+                       _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_void],
+    "ember_gate_mul": [_c_void, _c_void, ctypes.c_longlong, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ember_mlstm_gates": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
+    "ember_mlstm_scan": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
+                         _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
+    "ember_mingru": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
+                     _c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_int, _c_void],
     "ember_sample": [_c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_float, _c_u64, _c_void, _c_void, _c_u64, _c_void],
 }
 
@@ -161,6 +173,8 @@ def load_library() -> ctypes.CDLL:
     lib.ember_delta_rule_scratch.restype = _c_size
     lib.ember_attention_decode_kept_scratch.argtypes = [_c_int] * 4
     lib.ember_attention_decode_kept_scratch.restype = _c_size
+    lib.ember_mingru_scratch.argtypes = [_c_int] * 3
+    lib.ember_mingru_scratch.restype = _c_size
     for name in ("ember_tc_status", "ember_linear_decode_status", "ember_attention_decode_status",
                  "ember_attention_decode_mma_status"):
         getattr(lib, name).argtypes = []
@@ -324,10 +338,10 @@ class CudaOps:
         return copy
 
     # ------------------------------------------------------------------ rows
-    def embed(self, tokens, positions, table, pos_table, token_src=None, ids=None):
+    def embed(self, tokens, positions, table, pos_table, token_src=None, ids=None, token_scale: float = 1.0):
         """Rows of the token table (plus rows of the position table) in float32.  With `token_src` and `ids`
         (int32, on the device) token t is ids[token_src[t]] where token_src[t] >= 0: an id that an earlier
-        step's sampler left there."""
+        step's sampler left there.  `token_scale` multiplies the token's row alone, before the position's is added."""
         T, d = tokens.shape[0], table.shape[1]
         if pos_table is not None and (pos_table.dtype != table.dtype or pos_table.shape[1] != d):
             raise KernelError("embed: the position table must have the token table's type and width")
@@ -338,7 +352,7 @@ class CudaOps:
         x = torch.empty((T, d), dtype=torch.float32, device=table.device)
         self._call("ember_embed", tokens.data_ptr(), positions.data_ptr(), self._dense(table, "token table").data_ptr(),
                    self._ptr(pos_table), x.data_ptr(), T, d, _code(table.dtype), self._ptr(token_src), self._ptr(ids),
-                   0 if ids is None else ids.numel(), table.shape[0])
+                   0 if ids is None else ids.numel(), table.shape[0], float(token_scale))
         return x
 
     def warm(self, tensor) -> None:
@@ -458,6 +472,13 @@ class CudaOps:
         # A matrix that fills L2 by itself (a vocabulary head) streams faster through the tcgen05 kernel from 9
         # rows on (GPT-2 XL's head at 16 rows: 34.7 against 48.0 microseconds; at 8 rows 32.9 against 27.4).
         big = w.numel() * 2 > (64 << 20) and M > 8 and self.linear_stream_on
+        if act == "relu2" and not (M <= SMALL_M and K % 8 == 0 and K <= 16384 and not big):
+            # only the small product has this activation in its epilogue: the others run plain, the activation after them
+            if residual is not None:
+                raise KernelError("linear: an activation after the product cannot follow a residual sum")
+            out = self.linear(a, w, bias, None, None, out_dtype)
+            self._call("ember_act_inplace", out.data_ptr(), out.numel(), _ACT[act], _code(out.dtype))
+            return out
         if M <= SMALL_M and K % 8 == 0 and K <= 16384 and not big:
             # (Only a matrix that a part announced with `warm` is asked into L2 here.  Every product asking for the
             # next announced matrix paid at 8 rows once, 1.556 -> 1.512 ms a step of GPT-2 XL, and costs since the
@@ -581,7 +602,7 @@ class CudaOps:
                    _code(qkv.dtype))
 
     def attention(self, qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype, store=False,
-                  keep_first=None, value_dim=None):
+                  keep_first=None, value_dim=None, slopes=None, sinks=None):
         """Causal attention of the step's tokens over the cache.  With `store` their own keys and
         values are written into the cache first (in the same launch where a kernel can).
         float32: the plain kernel, whose sums depend on positions alone.  bfloat16: one token per
@@ -589,13 +610,19 @@ class CudaOps:
         the plain kernel for head sizes that one has no instantiation for.
         keep_first / value_dim (a mixer that keeps a sequence's first positions visible beside its
         window, or whose values have a row size of their own): the plain kernel, which knows both and
-        every head size, or for prompts in bfloat16 the mma.sync kernel where it has the head size."""
+        every head size, or for prompts in bfloat16 the mma.sync kernel where it has the head size.
+        slopes (float32 per query head): the score of a key loses slopes[h] times its distance to the query.
+        sinks (float32 per query head): the softmax's denominator also holds exp(sinks[h]), a term without a
+        key or a value.  Both go the way of keep_first / value_dim."""
         if qkv.dtype != cache.k.dtype or out_dtype != qkv.dtype:
             raise KernelError("attention: activations, cache and output have one element type")
         self._dense(qkv, "qkv")
-        if keep_first is not None or value_dim is not None:
+        for name, t in (("slopes", slopes), ("sinks", sinks)):
+            if t is not None and (t.dtype != torch.float32 or tuple(t.shape) != (n_heads,) or not t.is_cuda):
+                raise KernelError(f"attention: {name} are float32 values, one a query head")
+        if keep_first is not None or value_dim is not None or slopes is not None or sinks is not None:
             return self._attention_kept(qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype, store,
-                                        int(keep_first or 0), head_dim if value_dim is None else int(value_dim))
+                                        int(keep_first or 0), head_dim if value_dim is None else int(value_dim), slopes, sinks)
         out = torch.empty((plan.T, n_heads * head_dim), dtype=out_dtype, device=qkv.device)
         pages = plan.pages[cache.group_index]
         if qkv.dtype == torch.bfloat16 and plan.all_single:
@@ -649,7 +676,8 @@ class CudaOps:
                    float(scale), int(window), _code(qkv.dtype))
         return out
 
-    def _attention_kept(self, qkv, cache, plan, n_heads, kv_heads, hd, scale, window, out_dtype, store, keep_first, vd):
+    def _attention_kept(self, qkv, cache, plan, n_heads, kv_heads, hd, scale, window, out_dtype, store, keep_first, vd,
+                        slopes=None, sinks=None):
         if qkv.shape[1] != (n_heads + kv_heads) * hd + kv_heads * vd:
             raise KernelError(f"attention: rows of {qkv.shape[1]} values are not q | k | v of {n_heads} x {hd}, "
                               f"{kv_heads} x {hd} and {kv_heads} x {vd}")
@@ -662,6 +690,9 @@ class CudaOps:
                        plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), pages.data_ptr(), plan.max_blocks, plan.T,
                        n_heads, kv_heads, hd, vd, _code(qkv.dtype))
         fast = self.attention_kept_fast and qkv.dtype == torch.bfloat16
+        biased = slopes is not None or sinks is not None
+        if biased:
+            fast = False
         if fast and plan.all_single and plan.T == plan.n:
             # one token each: the visible keys in chunks of 128, a block a chunk and key/value head, then the merge
             max_keys = min(keep_first + window, plan.max_end) if window > 0 else plan.max_end
@@ -681,10 +712,10 @@ class CudaOps:
                             kv_heads, hd, float(scale), int(window), keep_first, allow=(2,))
             if rc == 0:
                 return out
-        self._call("ember_attention_plain_v", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), out.data_ptr(),
+        self._call("ember_attention_plain_biased", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), out.data_ptr(),
                    plan.positions.data_ptr(), plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), pages.data_ptr(),
                    plan.max_blocks, plan.T, n_heads, kv_heads, hd, float(scale), int(window), vd, keep_first,
-                   _code(qkv.dtype))
+                   self._ptr(slopes), self._ptr(sinks), _code(qkv.dtype))
         return out
 
     # ------------------------------------------------------------------ branches side by side
@@ -818,16 +849,135 @@ class CudaOps:
                    self._ptr(scratch), _code(xbc.dtype))
         return y
 
-    def gated_group_norm(self, y, proj, z_col, w, parts, eps, out_dtype, gate_first=True):
+    def gated_group_norm(self, y, proj, z_col, w, parts, eps, out_dtype, gate_first=True, gate="silu"):
         """unit(y * silu(z)) * w with the root mean square over each of `parts` equal pieces of a row; z: the
-        columns from z_col of `proj`.  gate_first False: unit(y) * w * silu(z), the gate after the norm."""
+        columns from z_col of `proj`.  gate_first False: unit(y) * w * silu(z), the gate after the norm.
+        gate "sigmoid": sigmoid(z) in place of silu(z)."""
+        if gate not in ("silu", "sigmoid"):
+            raise KernelError(f"gated_group_norm: gate {gate!r}")
         rows, n = y.shape
         if y.dtype != torch.float32 or proj.dtype != out_dtype or z_col + n > proj.shape[1] or w.shape[0] != n:
             raise KernelError("gated_group_norm: float32 y, the gate in the output's element type, a gain of y's width")
         out = torch.empty((rows, n), dtype=out_dtype, device=y.device)
         z = proj[:, z_col:]
         self._call("ember_gated_group_norm", self._dense(y, "y").data_ptr(), z.data_ptr(), proj.stride(0), w.data_ptr(),
-                   out.data_ptr(), rows, n, int(parts), float(eps), 1 if gate_first else 0, _code(out_dtype))
+                   out.data_ptr(), rows, n, int(parts), float(eps), (1 if gate_first else 0) | (2 if gate == "sigmoid" else 0),
+                   _code(out_dtype))
+        return out
+
+
+    # ------------------------------------------------------------------ branches with norms of their own, gates
+    def add_branches(self, x, branches, gain, eps):
+        """x += gain * sum of factor * b over `branches` in place, one launch.  A branch is (rows, factor) or
+        (rows, factor, w): with w (a float32 gain of the row's width) the rows are divided by their root mean square
+        and multiplied by w first.  gain: float32 per channel, or None."""
+        rows, d = x.shape
+        if x.dtype != torch.float32 or not x.is_contiguous():
+            raise KernelError("add_branches: a contiguous float32 stream")
+        n = len(branches)
+        if not 1 <= n <= 8:
+            raise KernelError(f"add_branches: {n} branches (1 to 8)")
+        norms = []
+        for b in branches:
+            t, w = b[0], (b[2] if len(b) > 2 else None)
+            if t.dtype != torch.float32 or tuple(t.shape) != (rows, d) or t.stride(1) != 1 or not t.is_cuda:
+                raise KernelError("add_branches: every branch is float32 [rows, width] with contiguous rows")
+            if w is not None and (w.dtype != torch.float32 or tuple(w.shape) != (d,)):
+                raise KernelError("add_branches: a branch's gain is float32 of the row's width")
+            norms.append(w)
+        if gain is not None and (gain.dtype != torch.float32 or tuple(gain.shape) != (d,)):
+            raise KernelError("add_branches: the gain is float32 of the row's width")
+        ptrs = (_c_void * n)(*[b[0].data_ptr() for b in branches])
+        strides = (ctypes.c_longlong * n)(*[b[0].stride(0) for b in branches])
+        factors = (_c_float * n)(*[float(b[1]) for b in branches])
+        gains = (_c_void * n)(*[self._ptr(w) for w in norms])
+        self._call("ember_add_branches", x.data_ptr(), ctypes.cast(ptrs, _c_void), ctypes.cast(strides, _c_void),
+                   ctypes.cast(factors, _c_void), ctypes.cast(gains, _c_void), n, self._ptr(gain), rows, d, float(eps))
+        return x
+
+    def qkv_norm(self, proj, positions, heads, kv_heads, head_dim, value_dim, out_dtype, q_gain=None, k_gain=None,
+                 unit_values=False, eps=0.0, temp_coef=0.0, temp_every=1):
+        """The first columns of `proj` (q | k | v) as packed rows of `out_dtype`: q and k each divided by their root mean
+        square over the whole row of heads and multiplied by a gain (where one is given), q then by the temperature
+        1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) of its position p, and every value head divided by its own root
+        mean square (`unit_values`)."""
+        T = proj.shape[0]
+        q_w, k_w = heads * head_dim, kv_heads * head_dim
+        width = q_w + k_w + kv_heads * value_dim
+        if proj.shape[1] < width or proj.stride(1) != 1:
+            raise KernelError("qkv_norm: rows too short for q | k | v")
+        for name, g, n in (("q", q_gain, q_w), ("k", k_gain, k_w)):
+            if g is not None and (g.dtype != torch.float32 or tuple(g.shape) != (n,)):
+                raise KernelError(f"qkv_norm: the gain of {name} is float32 of its width")
+        out = torch.empty((T, width), dtype=out_dtype, device=proj.device)
+        self._call("ember_qkv_norm", proj.data_ptr(), proj.stride(0), out.data_ptr(), positions.data_ptr(), self._ptr(q_gain),
+                   self._ptr(k_gain), T, q_w, k_w, kv_heads, value_dim, 1 if unit_values else 0, float(eps), float(temp_coef),
+                   int(temp_every), _code(proj.dtype), _code(out_dtype))
+        return out
+
+    def gate_mul(self, a, proj, z_col, gate="sigmoid"):
+        """a * gate(z), z the columns from z_col of `proj`; gate "sigmoid" or "silu"."""
+        rows, n = a.shape
+        if gate not in ("silu", "sigmoid") or z_col + n > proj.shape[1] or proj.shape[0] != rows:
+            raise KernelError("gate_mul: the gate's columns do not fit")
+        out = torch.empty_like(a)
+        z = proj[:, z_col:]
+        self._call("ember_gate_mul", self._dense(a, "gated rows").data_ptr(), z.data_ptr(), proj.stride(0), out.data_ptr(), rows, n,
+                   1 if gate == "sigmoid" else 0, _code(a.dtype), _code(proj.dtype))
+        return out
+
+    # ------------------------------------------------------------------ mLSTM, minGRU
+    def mlstm_gates(self, h, w, bias, heads, cap):
+        """float32 [T, 2 * heads]: the heads' log input gates cap * tanh((h w_i + b_i) / cap), then their log forget gates
+        logsigmoid(cap * tanh((h w_f + b_f) / cap)); w [2 * heads, width] in h's element type, bias float32."""
+        T, width = h.shape
+        if w.dtype != h.dtype or tuple(w.shape) != (2 * heads, width) or bias.dtype != torch.float32 or bias.shape[0] != 2 * heads:
+            raise KernelError("mlstm_gates: the gates' rows in the input's element type and a float32 bias")
+        gates = torch.empty((T, 2 * heads), dtype=torch.float32, device=h.device)
+        self._call("ember_mlstm_gates", self._dense(h, "mixer input").data_ptr(), self._dense(w, "gate rows").data_ptr(),
+                   bias.data_ptr(), gates.data_ptr(), T, heads, width, float(cap), _code(h.dtype))
+        return gates
+
+    def mlstm_scan(self, proj, q_col, k_col, v_col, gates, state, plan, heads, dim, vdim, floor):
+        """The recurrence of parts/mlstm.py over the step's sequences: q, k (heads x dim) and v (heads x vdim) are
+        columns of `proj`; state: {"S": [slots, heads, dim, vdim], "n": [slots, heads, dim], "m": [slots, heads]}
+        float32 (advanced); float32 [T, heads * vdim]."""
+        S, n, m = state["S"], state["n"], state["m"]
+        if (S.dtype != torch.float32 or tuple(S.shape[1:]) != (heads, dim, vdim) or tuple(n.shape[1:]) != (heads, dim)
+                or tuple(m.shape[1:]) != (heads,)):
+            raise KernelError("mlstm_scan: the state is float32 S [slots, heads, dim, vdim], n [slots, heads, dim], m [slots, heads]")
+        if gates.dtype != torch.float32 or tuple(gates.shape) != (plan.T, 2 * heads):
+            raise KernelError("mlstm_scan: float32 log gates [T, 2 * heads]")
+        if max(q_col, k_col) + heads * dim > proj.shape[1] or v_col + heads * vdim > proj.shape[1]:
+            raise KernelError("mlstm_scan: the columns of q, k and v do not fit the rows")
+        out = torch.empty((plan.T, heads * vdim), dtype=torch.float32, device=proj.device)
+        self._call("ember_mlstm_scan", proj.data_ptr(), proj.stride(0), int(q_col), int(k_col), int(v_col), gates.data_ptr(),
+                   S.data_ptr(), n.data_ptr(), m.data_ptr(), out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(),
+                   plan.cu_new.data_ptr(), plan.n, heads, dim, vdim, float(floor), _code(proj.dtype))
+        return out
+
+    MINGRU_PIECE = 128      # tokens of a piece when a long sequence's recurrence is walked in pieces side by side
+
+    def mingru(self, proj, z_col, x_col, g_col, bias_z, bias_x, state, plan, width, out_dtype, pieces=None):
+        """The recurrence of parts/mingru.py over the step's sequences: the gate's, the candidate's and the output gate's
+        columns of `proj`; state float32 [slots, width] (advanced); S_t * silu(g_t) as [T, width] of `out_dtype`."""
+        if state.dtype != torch.float32 or tuple(state.shape[1:]) != (width,):
+            raise KernelError("mingru: the state is float32 [slots, width]")
+        if max(z_col, x_col, g_col) + width > proj.shape[1]:
+            raise KernelError("mingru: the columns do not fit the rows")
+        out = torch.empty((plan.T, width), dtype=out_dtype, device=proj.device)
+        longest = max(int(plan.max_new), 1)
+        if pieces is None:
+            pieces = -(-longest // self.MINGRU_PIECE) if longest >= 4 * self.MINGRU_PIECE else 1
+        piece = -(-longest // pieces)
+        scratch = None
+        if pieces > 1:
+            scratch = torch.empty(self.lib.ember_mingru_scratch(plan.n, pieces, width), dtype=torch.float32, device=proj.device)
+        self._call("ember_mingru", proj.data_ptr(), proj.stride(0), int(z_col), int(x_col), int(g_col), bias_z.data_ptr(),
+                   bias_x.data_ptr(), state.data_ptr(), out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(),
+                   plan.cu_new.data_ptr(), plan.n, width, piece, pieces, self._ptr(scratch), _code(proj.dtype), _code(out_dtype))
+        if pieces > 1:
+            self.launches += 2
         return out
 
     # ------------------------------------------------------------------ a table of token pairs

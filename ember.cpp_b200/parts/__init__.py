@@ -3,7 +3,7 @@ that a ModelSpec puts together from them.  Importing this package registers the 
 from .base import (Block, CacheNeed, EmbedPart, FeedForward, Mixer, Norm, Part, Position, StateNeed, WeightSpec, build_block,
                    build_part, register_part, registered)
 from .spec import Application, LayerSpec, ModelSpec, PartSpec
-from . import attention, block, delta, embed, latent, mlp, moe, norm, parallel, position, ssm  # noqa: F401  (register the built-in kinds)
+from . import attention, block, delta, embed, latent, mingru, mlp, mlstm, moe, norm, parallel, position, ssm  # noqa: F401  (register the built-in kinds)
 from .model import DecoderModel
 
 __all__ = ["Application", "Block", "CacheNeed", "DecoderModel", "EmbedPart", "FeedForward", "LayerSpec", "Mixer", "ModelSpec", "Norm",

@@ -14,6 +14,17 @@ visible beside the window (query p sees key j <= p if p - j < window or j < keep
 keeps their pages); values may have a row size of their own (`value_dim`); q, k and v may be
 stored as three matrices (`qkv` a tuple of three names: they are laid end to end at load, so the
 step still makes one product); tensor names may carry no `.weight` suffix (`suffix`).
+
+Further options, each off by default and each a parameter (`parts/attention.py::CausalAttention`):
+`qk_norm` = (name of q's gain, name of k's gain): q and k are each divided by their root mean square over
+the whole projection, before they are cut into heads, and multiplied by a gain of that size; `value_norm`:
+every value head is divided by its own root mean square before it is cached; `q_temp` = (coef, every): q at
+position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1); `distance_slope_base` = b: the score of
+key j for query i of head h loses 2^(-b (h + 1) / heads) * (i - j); `sink`: the name of one learned number per
+head whose exponential is added to the softmax's denominator (it has no key and no value); `gate`: the name of a
+matrix W_g, the heads laid end to end are multiplied by sigmoid(W_g h) before the output projection.  With a norm
+on q or k or v, or a gate, the projection q | k | v (| g) is left in float32 (the norms read it unrounded) and
+the normed rows are rounded to the compute type once.
 """
 from __future__ import annotations
 
@@ -25,7 +36,9 @@ class CausalAttention(Mixer):
     def __init__(self, prefix: str, width: int, n_heads: int, kv_heads: int, head_dim: int, scale: float,
                  window: int = 0, qkv="c_attn", out: str = "c_proj", stored: str = "in_out",
                  bias: bool = True, init_std: float = 0.02, out_init_std: float = 0.02, bias_init_std: float = 0.01,
-                 keep_first: int = 0, value_dim: int | None = None, suffix: str = ".weight"):
+                 keep_first: int = 0, value_dim: int | None = None, suffix: str = ".weight", qk_norm=None,
+                 value_norm: bool = False, norm_eps: float = 0.0, q_temp=None, distance_slope_base: float | None = None,
+                 sink: str | None = None, gate: str | None = None):
         super().__init__(prefix)
         if n_heads % kv_heads:
             raise ValueError(f"attention {prefix!r}: {n_heads} heads are not a multiple of {kv_heads} key/value heads")
@@ -36,7 +49,20 @@ class CausalAttention(Mixer):
         self.width, self.n_heads, self.kv_heads, self.head_dim = int(width), int(n_heads), int(kv_heads), int(head_dim)
         self.scale, self.window, self.keep_first = float(scale), int(window), int(keep_first)
         # keep_first or an explicit value size take the kernels that know both (and every head size, also in bfloat16)
-        self.extended = int(keep_first) > 0 or value_dim is not None
+        self.qk_norm_names = None if qk_norm is None else tuple(prefix + n for n in qk_norm)
+        self.value_norm, self.norm_eps = bool(value_norm), float(norm_eps)
+        self.q_temp = None if q_temp is None else (float(q_temp[0]), int(q_temp[1]))
+        if self.q_temp is not None and self.q_temp[1] <= 0:
+            raise ValueError(f"attention {prefix!r}: a temperature that grows every {self.q_temp[1]} positions")
+        self.slope_base = None if distance_slope_base is None else float(distance_slope_base)
+        self.sink_name = None if sink is None else prefix + sink
+        self.gate_name = None if gate is None else prefix + gate
+        # rows that pass a norm, a temperature or a gate between the projection and the attention
+        self.prepared = self.qk_norm_names is not None or self.value_norm or self.q_temp is not None or self.gate_name is not None
+        self.biased = self.slope_base is not None or self.sink_name is not None
+        if (self.prepared or self.biased) and bias:
+            raise ValueError(f"attention {prefix!r}: norms, gates, slopes and sinks come without biases")
+        self.extended = int(keep_first) > 0 or value_dim is not None or self.prepared or self.biased
         self.value_dim = self.head_dim if value_dim is None else int(value_dim)
         if not 1 <= self.value_dim <= 256:
             raise ValueError(f"attention {prefix!r}: value size {self.value_dim} is not in [1, 256]")
@@ -53,6 +79,7 @@ class CausalAttention(Mixer):
         self.widths = (self.q_width, self.kv_heads * self.head_dim, self.kv_heads * self.value_dim)
         self.qkv_width = sum(self.widths)
         self.w_qkv = self.b_qkv = self.w_out = self.b_out = None
+        self.q_gain = self.k_gain = self.sinks = self.slopes = None
 
     def _shape(self, n_in, n_out):
         return (n_in, n_out) if self.stored == "in_out" else (n_out, n_in)
@@ -67,6 +94,13 @@ class CausalAttention(Mixer):
         if self.bias:
             specs += [WeightSpec(self.qkv_name + ".bias", (self.qkv_width,), std=self.bias_init_std),
                       WeightSpec(self.out_name + ".bias", (self.width,), std=self.bias_init_std)]
+        if self.qk_norm_names is not None:
+            specs += [WeightSpec(self.qk_norm_names[0], (self.q_width,), mean=1.0, std=0.1),
+                      WeightSpec(self.qk_norm_names[1], (self.widths[1],), mean=1.0, std=0.1)]
+        if self.sink_name is not None:
+            specs.append(WeightSpec(self.sink_name, (self.n_heads,), std=1.0))
+        if self.gate_name is not None:
+            specs.append(WeightSpec(self.gate_name + self.suffix, self._shape(self.width, self.o_width), std=self.init_std))
         return specs
 
     def load(self, get, runtime):
@@ -82,6 +116,17 @@ class CausalAttention(Mixer):
         else:
             self.w_qkv = runtime.matrix(get(self.qkv_name + self.suffix), transpose=t)
         self.w_out = runtime.matrix(get(self.out_name + self.suffix), transpose=t)
+        if self.gate_name is not None:      # the gate's rows under q | k | v, each part from a multiple of 8 columns on
+            self.gate_col = -(-self.qkv_width // 8) * 8
+            pad = torch.zeros((self.gate_col - self.qkv_width, self.width), dtype=self.w_qkv.dtype, device=self.w_qkv.device)
+            self.w_qkv = torch.cat([self.w_qkv, pad, runtime.matrix(get(self.gate_name + self.suffix), transpose=t)]).contiguous()
+        if self.qk_norm_names is not None:
+            self.q_gain, self.k_gain = (runtime.vector(get(n)) for n in self.qk_norm_names)
+        if self.sink_name is not None:
+            self.sinks = runtime.vector(get(self.sink_name))
+        if self.slope_base is not None:
+            self.slopes = torch.tensor([2.0 ** (-self.slope_base * (h + 1) / self.n_heads) for h in range(self.n_heads)],
+                                       dtype=torch.float32, device=self.w_qkv.device)
         if self.bias:
             self.b_qkv = runtime.vector(get(self.qkv_name + ".bias"))
             self.b_out = runtime.vector(get(self.out_name + ".bias"))
@@ -96,6 +141,18 @@ class CausalAttention(Mixer):
 
     def _attend(self, ctx, h, app):
         ops = ctx.ops
+        if self.prepared:
+            import torch
+            proj = ops.linear(h, self.w_qkv, None, out_dtype=torch.float32)          # float32 [T, q | k | v (| 0 | g)]
+            coef, every = self.q_temp or (0.0, 1)
+            qkv = ops.qkv_norm(proj, ctx.plan.positions, self.n_heads, self.kv_heads, self.head_dim, self.value_dim, ctx.dtype,
+                               q_gain=self.q_gain, k_gain=self.k_gain, unit_values=self.value_norm, eps=self.norm_eps,
+                               temp_coef=coef, temp_every=every)
+            ctx.position.apply_qk(ctx, qkv, self.n_heads, self.kv_heads, self.head_dim)
+            o = ops.attention(qkv, app.cache, ctx.plan, self.n_heads, self.kv_heads, self.head_dim, self.scale, self.window,
+                              out_dtype=ctx.dtype, store=app.writes_cache, keep_first=self.keep_first if self.window > 0 else 0,
+                              value_dim=self.value_dim, slopes=self.slopes, sinks=self.sinks)
+            return o if self.gate_name is None else ops.gate_mul(o, proj, self.gate_col, "sigmoid")
         qkv = ops.linear(h, self.w_qkv, self.b_qkv, out_dtype=ctx.dtype)
         ctx.position.apply_qk(ctx, qkv, self.n_heads, self.kv_heads, self.head_dim)
         if not self.extended:
@@ -103,7 +160,8 @@ class CausalAttention(Mixer):
                                  self.window, out_dtype=ctx.dtype, store=app.writes_cache)
         return ops.attention(qkv, app.cache, ctx.plan, self.n_heads, self.kv_heads, self.head_dim, self.scale,
                              self.window, out_dtype=ctx.dtype, store=app.writes_cache,
-                             keep_first=self.keep_first if self.window > 0 else 0, value_dim=self.value_dim)
+                             keep_first=self.keep_first if self.window > 0 else 0, value_dim=self.value_dim,
+                             slopes=self.slopes, sinks=self.sinks)
 
     def forward(self, ctx, h, residual, app):
         return ctx.ops.linear(self._attend(ctx, h, app), self.w_out, self.b_out, residual=residual)

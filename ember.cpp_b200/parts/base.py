@@ -11,7 +11,10 @@ Roles and what each must provide:
   ffn       forward(ctx, h, residual) -> new residual stream
             (mixer and ffn also: branches(ctx, h[, app]) -> [(float32 rows, factor)], the output as a weighted
             sum that the caller adds itself, for arrangements that norm a sublayer's output before the sum;
-            a norm's add_normed(ctx, x, branches) makes that sum, norms it and adds it to the stream)
+            a norm's add_normed(ctx, x, branches) makes that sum, norms it and adds it to the stream.  A branch
+            may carry a third entry (gain, eps): its rows are then divided by their root mean square and
+            multiplied by that gain before they are weighted; `plain_branches` does that for a consumer that has
+            no kernel for it)
   embed     forward(ctx, x, state) -> x     (adds to the embedded rows; state_need() as a mixer's: what it
             carries per sequence, kept by the cache beside the layers' states)
   position  embedding_table() -> tensor | None, max_positions() -> int | None,
@@ -91,6 +94,19 @@ class Part:
         runtime's device) and keep them in the form the kernels want."""
 
 
+def plain_branches(ctx, branches):
+    """`branches` with every pending norm of a branch's own carried out: [(float32 rows, factor)]."""
+    import torch
+    out = []
+    for b in branches:
+        if len(b) > 2 and b[2] is not None:
+            gain, eps = b[2]
+            out.append((ctx.ops.rmsnorm(b[0].contiguous(), gain, eps, torch.float32), b[1]))
+        else:
+            out.append((b[0], b[1]))
+    return out
+
+
 class Norm(Part):
     role = "norm"
 
@@ -101,7 +117,7 @@ class Norm(Part):
         """x + norm(sum of factor * rows over `branches`), the sums in float32.  A norm whose kernel
         does all of it in one launch overrides this."""
         total = None
-        for rows, factor in branches:
+        for rows, factor in plain_branches(ctx, branches):
             term = rows.float() * factor
             total = term if total is None else total + term
         return x + self.forward(ctx, total.contiguous(), x.dtype)

@@ -14,7 +14,7 @@ from __future__ import annotations
 
 from .base import FeedForward, WeightSpec, register_part
 
-ACTIVATIONS = ("gelu_tanh", "gelu_erf")
+ACTIVATIONS = ("gelu_tanh", "gelu_erf", "relu2")     # relu2: the square of relu
 
 
 class DenseFeedForward(FeedForward):
@@ -66,6 +66,11 @@ class DenseFeedForward(FeedForward):
             warm(self.w_down)  # a hint: the second product's weights can be on their way during the first
         u = ctx.ops.linear(h, self.w_up, self.b_up, act=self.activation, out_dtype=ctx.dtype)
         return ctx.ops.linear(u, self.w_down, self.b_down, residual=residual)
+
+    def branches(self, ctx, h):
+        import torch
+        u = ctx.ops.linear(h, self.w_up, self.b_up, act=self.activation, out_dtype=ctx.dtype)
+        return [(ctx.ops.linear(u, self.w_down, self.b_down, out_dtype=torch.float32), 1.0)]
 
 
 GATES = ("silu", "clamped_sigmoid")

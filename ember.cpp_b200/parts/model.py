@@ -109,13 +109,16 @@ class DecoderModel:
             # a part looks its tokens up in a table of its own: the ids are put into the description first
             ops.take_tokens(plan.tokens, plan.token_src, ids, self.spec.vocab_size)
             ids = None
+        scale = self.spec.embedding_scale
+        in_kernel = scale != 1.0 and not self.spec.scale_positions    # the factor on the token's row alone: the embedding's own
+        more = {"token_scale": scale} if in_kernel else {}
         if ids is not None:
             x = ops.embed(plan.tokens, plan.positions, self.table, self.position.embedding_table(),
-                          token_src=plan.token_src, ids=ids)
+                          token_src=plan.token_src, ids=ids, **more)
         else:
-            x = ops.embed(plan.tokens, plan.positions, self.table, self.position.embedding_table())
-        if self.spec.embedding_scale != 1.0:
-            x = ops.scale_cap(x, scale=self.spec.embedding_scale)
+            x = ops.embed(plan.tokens, plan.positions, self.table, self.position.embedding_table(), **more)
+        if scale != 1.0 and not in_kernel:
+            x = ops.scale_cap(x, scale=scale)
         for i, part in enumerate(self.embed_parts):
             x = part.forward(ctx, x, self._embed_state(ctx, i, part))
         if self.embed_norm is not None:
@@ -130,6 +133,6 @@ class DecoderModel:
         rows = x if plan.wants_every_row else ops.gather_rows(x, plan.want_rows, plan.n_want)
         h = self.final_norm.forward(ctx, rows, ctx.dtype)
         logits = ops.linear(h, self.head, self.head_bias, out_dtype=torch.float32)
-        if self.spec.logit_cap is not None:
-            logits = ops.scale_cap(logits, cap=self.spec.logit_cap)
+        if self.spec.logit_cap is not None or self.spec.logit_scale != 1.0:
+            logits = ops.scale_cap(logits, scale=self.spec.logit_scale, cap=self.spec.logit_cap)
         return logits

@@ -58,6 +58,8 @@ class ModelSpec:
     final_norm: PartSpec
     head: str | None                 # tensor name of the [vocab, width] head; None: tied to the token table
     embedding_scale: float = 1.0     # the embedded rows are multiplied by this (a model that scales by sqrt(width))
+    scale_positions: bool = True     # False: the factor is on the token's row alone, a position table's row is added as it is
+    logit_scale: float = 1.0         # the logits are multiplied by this (before a cap)
     head_bias: str | None = None     # tensor name of a [vocab] bias added to the logits
     logit_cap: float | None = None   # logits become cap * tanh(logits / cap)
     table_init_std: float = 0.02     # random-weights mode: std of the token table and the head

@@ -17,8 +17,8 @@ PAGE = 64
 class CpuOps:
     name = "cpu-double"
 
-    def embed(self, tokens, positions, table, pos_table):
-        x = table[tokens.long()].float()
+    def embed(self, tokens, positions, table, pos_table, token_scale=1.0):
+        x = table[tokens.long()].float() * token_scale
         if pos_table is not None:
             x = x + pos_table[positions.long()].float()
         return x
@@ -37,6 +37,8 @@ class CpuOps:
             y = 0.5 * y * (1 + torch.tanh(math.sqrt(2 / math.pi) * (y + 0.044715 * y ** 3)))
         elif act == "gelu_erf":
             y = 0.5 * y * (1 + torch.erf(y / math.sqrt(2)))
+        elif act == "relu2":
+            y = torch.relu(y) ** 2
         elif act is not None:
             raise ValueError(act)
         if residual is not None:
@@ -65,7 +67,8 @@ class CpuOps:
             cache.v[page, :, p % PAGE, :] = qkv[t, q_w + kv_w:q_w + kv_w + kv_heads * vd].view(kv_heads, vd).to(cache.v.dtype)
 
     def attention(self, qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype, store=False,
-                  keep_first=0, value_dim=None):
+                  keep_first=0, value_dim=None, slopes=None, sinks=None):
+        keep_first = keep_first or 0
         if store:
             self.kv_store(qkv, cache, plan, n_heads, kv_heads, head_dim, value_dim)
         g = cache.group_index
@@ -88,7 +91,12 @@ class CpuOps:
             q = qkv[t, :n_heads * head_dim].float().view(n_heads, head_dim)
             for h in range(n_heads):
                 sc = (k[:, h // rep, :] @ q[h]) * scale
-                pr = torch.softmax(sc, 0)
+                if slopes is not None:
+                    sc = sc - slopes[h] * (p - pos).float()
+                if sinks is not None:       # one more term of the denominator, without a value
+                    pr = torch.softmax(torch.cat([sc, sinks[h:h + 1]]), 0)[:-1]
+                else:
+                    pr = torch.softmax(sc, 0)
                 out[t, h * vd:(h + 1) * vd] = pr @ v[:, h // rep, :]
         return out.to(out_dtype)
 
@@ -157,13 +165,90 @@ class CpuOps:
             state[slot] = S
         return y
 
-    def gated_group_norm(self, y, proj, z_col, w, parts, eps, out_dtype, gate_first=True):
+    def gated_group_norm(self, y, proj, z_col, w, parts, eps, out_dtype, gate_first=True, gate="silu"):
         n = y.shape[1]
         z = proj[:, z_col:z_col + n].float()
-        gate = z * torch.sigmoid(z)
+        gate = torch.sigmoid(z) if gate == "sigmoid" else z * torch.sigmoid(z)
         g = (y * gate if gate_first else y).view(y.shape[0], parts, n // parts)
         g = (g * torch.rsqrt((g * g).mean(-1, keepdim=True) + eps)).reshape(y.shape[0], n) * w
         return (g if gate_first else g * gate).to(out_dtype)
+
+    # ------------------------------------------------------------------ branches with norms of their own, gates
+    def add_branches(self, x, branches, gain, eps):
+        total = torch.zeros_like(x)
+        for b in branches:
+            rows = b[0].float()
+            if len(b) > 2 and b[2] is not None:
+                rows = rows * torch.rsqrt((rows * rows).mean(-1, keepdim=True) + eps) * b[2]
+            total += b[1] * rows
+        x += total if gain is None else gain * total
+        return x
+
+    def qkv_norm(self, proj, positions, heads, kv_heads, head_dim, value_dim, out_dtype, q_gain=None, k_gain=None,
+                 unit_values=False, eps=0.0, temp_coef=0.0, temp_every=1):
+        q_w, k_w = heads * head_dim, kv_heads * head_dim
+        unit = lambda t: t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps)  # noqa: E731
+        q, k = proj[:, :q_w].float(), proj[:, q_w:q_w + k_w].float()
+        v = proj[:, q_w + k_w:q_w + k_w + kv_heads * value_dim].float()
+        if q_gain is not None:
+            q = unit(q) * q_gain
+        if k_gain is not None:
+            k = unit(k) * k_gain
+        if temp_coef:
+            q = q * (1.0 + temp_coef * torch.log(((positions.long() + 1) // temp_every + 1).float()))[:, None]
+        if unit_values:
+            v = unit(v.view(-1, kv_heads, value_dim)).reshape(-1, kv_heads * value_dim)
+        return torch.cat([q, k, v], 1).to(out_dtype)
+
+    def gate_mul(self, a, proj, z_col, gate="sigmoid"):
+        z = proj[:, z_col:z_col + a.shape[1]].float()
+        return (a.float() * (torch.sigmoid(z) if gate == "sigmoid" else z * torch.sigmoid(z))).to(a.dtype)
+
+    # ------------------------------------------------------------------ mLSTM, minGRU
+    def mlstm_gates(self, h, w, bias, heads, cap):
+        g = h.float() @ w.float().t() + bias
+        if cap > 0:
+            g = cap * torch.tanh(g / cap)
+        return torch.cat([g[:, :heads], torch.nn.functional.logsigmoid(g[:, heads:])], 1)
+
+    def mlstm_scan(self, proj, q_col, k_col, v_col, gates, state, plan, heads, dim, vdim, floor):
+        out = torch.zeros(proj.shape[0], heads * vdim)
+        for slot, start, t0, t1 in self._sequences(plan):
+            if slot < 0:
+                continue
+            fresh = start == 0
+            S = torch.zeros(heads, dim, vdim) if fresh else state["S"][slot].clone()
+            n = torch.zeros(heads, dim) if fresh else state["n"][slot].clone()
+            m = torch.zeros(heads) if fresh else state["m"][slot].clone()
+            for t in range(t0, t1):
+                q = proj[t, q_col:q_col + heads * dim].float().view(heads, dim) * dim ** -0.5
+                k = proj[t, k_col:k_col + heads * dim].float().view(heads, dim)
+                v = proj[t, v_col:v_col + heads * vdim].float().view(heads, vdim)
+                li, lf = gates[t, :heads], gates[t, heads:]
+                m_new = torch.maximum(lf + m, li)
+                keep, take = torch.exp(lf + m - m_new), torch.exp(li - m_new)
+                S = keep[:, None, None] * S + take[:, None, None] * k[:, :, None] * v[:, None, :]
+                n = keep[:, None] * n + take[:, None] * k
+                m = m_new
+                den = torch.maximum((n * q).sum(-1).abs(), torch.exp(-m)) + floor
+                out[t] = (torch.einsum("hdv,hd->hv", S, q) / den[:, None]).reshape(-1)
+            state["S"][slot], state["n"][slot], state["m"][slot] = S, n, m
+        return out
+
+    def mingru(self, proj, z_col, x_col, g_col, bias_z, bias_x, state, plan, width, out_dtype, pieces=None):
+        out = torch.zeros(proj.shape[0], width)
+        for slot, start, t0, t1 in self._sequences(plan):
+            if slot < 0:
+                continue
+            S = state[slot].clone() if start > 0 else torch.zeros(width)
+            for t in range(t0, t1):
+                z = torch.sigmoid(proj[t, z_col:z_col + width].float() + bias_z)
+                u = proj[t, x_col:x_col + width].float() + bias_x
+                S = (1 - z) * S + z * torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+                g = proj[t, g_col:g_col + width].float()
+                out[t] = S * g * torch.sigmoid(g)
+            state[slot] = S
+        return out.to(out_dtype)
 
     # ------------------------------------------------------------------ a table of token pairs
     def pair_table_add(self, x, plan, table, state, mul_prev, mul_cur, buckets):
