@@ -9,6 +9,8 @@
 // all lanes at once); one maximum and one correction per head for the warp's 32 keys; then the 32 value rows
 // are walked through together, every lane owning a run of the value dims.  Softmax, sums and accumulators are
 // float32.  Partial results (m, l, acc[vd]) per (token, head, chunk) go to scratch that the caller gives.
+// With `slopes` the score of key j loses slopes[head] * (p - j); with `sinks` the merge adds exp(sinks[head]) to the
+// softmax's denominator (a term without a key or a value).
 #include "common.cuh"
 
 namespace {
@@ -23,7 +25,7 @@ decode_kept_partial_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfl
                            const __nv_bfloat16* __restrict__ vc, float* __restrict__ part,
                            const int* __restrict__ positions, const int* __restrict__ seq_slot,
                            const int* __restrict__ pages, int max_blocks, int n_heads, int kv_heads, int hd, int vd,
-                           float scale, int window, int keep_first, int n_chunks) {
+                           float scale, int window, int keep_first, int n_chunks, const float* __restrict__ slopes) {
   __shared__ float q_s[PER][256];
   __shared__ float m_s[kWarps][PER], l_s[kWarps][PER];
   __shared__ float acc_s[kWarps][PER][32 * DPL];
@@ -85,7 +87,8 @@ decode_kept_partial_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfl
   float pj[PER];
 #pragma unroll
   for (int h = 0; h < PER; ++h) {
-    const float s = valid ? sc[h] * scale : -INFINITY;
+    const float slope = slopes && h < per ? slopes[g * per + h] : 0.f;
+    const float s = valid ? sc[h] * scale - slope * (float)(p - j) : -INFINITY;
     const float m = warp_max(s);  // (the warp's first key is always there: m is finite)
     pj[h] = valid ? expf(s - m) : 0.f;
     const float l = warp_sum(pj[h]);
@@ -165,7 +168,8 @@ decode_kept_partial_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfl
 
 // grid (T * n_heads): out = sum_c e^(m_c - M) acc_c / sum_c e^(m_c - M) l_c, chunks in order
 __global__ void decode_kept_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out,
-                                         const int* __restrict__ seq_slot, int n_heads, int vd, int n_chunks) {
+                                         const int* __restrict__ seq_slot, int n_heads, int vd, int n_chunks,
+                                         const float* __restrict__ sinks) {
   const int item = blockIdx.x, t = item / n_heads;
   __nv_bfloat16* o = out + (size_t)item * vd;
   if (seq_slot[t] < 0) {
@@ -174,9 +178,9 @@ __global__ void decode_kept_merge_kernel(const float* __restrict__ part, __nv_bf
   }
   const size_t stride = (size_t)vd + 2;
   const float* src = part + (size_t)item * n_chunks * stride;
-  float m = -INFINITY;
+  float m = sinks ? sinks[item % n_heads] : -INFINITY;
   for (int c = 0; c < n_chunks; ++c) m = fmaxf(m, src[c * stride]);
-  float l = 0.f;
+  float l = sinks ? expf(sinks[item % n_heads] - m) : 0.f;
   for (int c = 0; c < n_chunks; ++c) {
     const float mc = src[c * stride];
     if (mc != -INFINITY) l = fmaf(src[c * stride + 1], expf(mc - m), l);
@@ -195,10 +199,10 @@ __global__ void decode_kept_merge_kernel(const float* __restrict__ part, __nv_bf
 template <int PER, int DPL>
 void launch_partial(dim3 grid, cudaStream_t stream, const void* qkv, const void* kc, const void* vc, float* part,
                     const int* positions, const int* seq_slot, const int* pages, int max_blocks, int n_heads,
-                    int kv_heads, int hd, int vd, float scale, int window, int keep_first, int n_chunks) {
+                    int kv_heads, int hd, int vd, float scale, int window, int keep_first, int n_chunks, const float* slopes) {
   launch_plain(decode_kept_partial_kernel<PER, DPL>, grid, dim3(32 * kWarps), 0, stream, (const __nv_bfloat16*)qkv,
              (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, part, positions, seq_slot, pages, max_blocks, n_heads,
-             kv_heads, hd, vd, scale, window, keep_first, n_chunks);
+             kv_heads, hd, vd, scale, window, keep_first, n_chunks, slopes);
 }
 
 }  // namespace
@@ -214,10 +218,27 @@ EMBER_API size_t ember_attention_decode_kept_scratch(int T, int n_heads, int vd,
 // length up to it).  Returns 2, having launched nothing, for sizes this kernel has no instantiation for
 // (more than 8 query heads a key/value head, values of more than 128 or of an odd size above 32, head sizes that
 // are no multiples of 8 or above 256): the caller then takes the plain kernel.
+EMBER_API int ember_attention_decode_biased(const void* qkv, const void* kc, const void* vc, void* out, float* scratch,
+                                            const int* positions, const int* seq_slot, const int* pages, int max_blocks,
+                                            int T, int n_heads, int kv_heads, int hd, int vd, float scale, int window,
+                                            int keep_first, int max_keys, const float* slopes, const float* sinks,
+                                            cudaStream_t stream);
+
 EMBER_API int ember_attention_decode_kept(const void* qkv, const void* kc, const void* vc, void* out, float* scratch,
                                           const int* positions, const int* seq_slot, const int* pages, int max_blocks,
                                           int T, int n_heads, int kv_heads, int hd, int vd, float scale, int window,
                                           int keep_first, int max_keys, cudaStream_t stream) {
+  return ember_attention_decode_biased(qkv, kc, vc, out, scratch, positions, seq_slot, pages, max_blocks, T, n_heads, kv_heads,
+                                       hd, vd, scale, window, keep_first, max_keys, nullptr, nullptr, stream);
+}
+
+// The same with a distance penalty (slopes: float32 per query head, or null) and a sink in the softmax's denominator
+// (sinks: float32 per query head, or null).
+EMBER_API int ember_attention_decode_biased(const void* qkv, const void* kc, const void* vc, void* out, float* scratch,
+                                            const int* positions, const int* seq_slot, const int* pages, int max_blocks,
+                                            int T, int n_heads, int kv_heads, int hd, int vd, float scale, int window,
+                                            int keep_first, int max_keys, const float* slopes, const float* sinks,
+                                            cudaStream_t stream) {
   EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0 && max_keys > 0, "attention_decode_kept: bad sizes");
   EMBER_CHECK(n_heads % kv_heads == 0, "attention_decode_kept: %d heads are not a multiple of %d key/value heads", n_heads,
               kv_heads);
@@ -233,7 +254,7 @@ EMBER_API int ember_attention_decode_kept(const void* qkv, const void* kc, const
   const int per_up = per <= 1 ? 1 : per <= 2 ? 2 : per <= 4 ? 4 : 8;
 #define EMBER_KEPT(PER, DPL)                                                                                              \
   launch_partial<PER, DPL>(grid, stream, qkv, kc, vc, scratch, positions, seq_slot, pages, max_blocks, n_heads, kv_heads, \
-                           hd, vd, scale, window, keep_first, n_chunks)
+                           hd, vd, scale, window, keep_first, n_chunks, slopes)
 #define EMBER_KEPT_PER(PER)          \
   do {                               \
     if (dpl == 1) EMBER_KEPT(PER, 1); \
@@ -248,7 +269,7 @@ EMBER_API int ember_attention_decode_kept(const void* qkv, const void* kc, const
 #undef EMBER_KEPT
   EMBER_LAUNCH_OK("attention_decode_kept");
   launch_plain(decode_kept_merge_kernel, dim3(T * n_heads), dim3(vd <= 32 ? 32 : (vd <= 64 ? 64 : 128)), 0, stream,
-             (const float*)scratch, (__nv_bfloat16*)out, seq_slot, n_heads, vd, n_chunks);
+             (const float*)scratch, (__nv_bfloat16*)out, seq_slot, n_heads, vd, n_chunks, sinks);
   EMBER_LAUNCH_OK("attention_decode_kept (merge)");
   return 0;
 }

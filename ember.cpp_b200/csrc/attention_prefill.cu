@@ -10,6 +10,8 @@
 // its window) are masked by selection, never by arithmetic on what the page holds.  With
 // `keep_first` > 0 the first positions of a sequence stay visible beside the window: the pages that
 // hold them and lie before the window's first page are taken first, then the window's pages.
+// With `slopes` the score of key j for the query at position i loses slopes[h] * (i - j); with `sinks`
+// the softmax's denominator also holds exp(sinks[h]): a row starts with that maximum and a sum of one.
 //
 // Head sizes: multiples of 16 up to 128 (one instantiation each); larger heads take the plain
 // kernel.
@@ -69,7 +71,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloa
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                          const int* __restrict__ seq_new, const int* __restrict__ cu_new,
                          const int* __restrict__ pages, int max_blocks, int n_heads, int kv_heads, float scale_log2,
-                         int window, int keep_first) {
+                         int window, int keep_first, const float* __restrict__ slopes, const float* __restrict__ sinks) {
   constexpr int LD = HD + 8, KS = HD / 16;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -115,7 +117,13 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloa
   for (int i = 0; i < 2 * KS; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  // (scores are kept as raw dot products, the scale joins them in the exponent: a slope and a sink are brought
+  // into those units by 1 / scale, which is log2(e) / scale_log2)
+  const float to_raw = 1.4426950408889634f / scale_log2;
+  const float slope_raw = slopes ? slopes[h] * to_raw : 0.f;
+  const float m_first = sinks ? sinks[h] * to_raw : -INFINITY;
+  const float l_first = sinks && (lane & 3) == 0 ? 1.f : 0.f;     // a row's sum lives in its four lanes: the sink's one in the first
+  float m_run[2] = {m_first, m_first}, l_run[2] = {l_first, l_first};
   const int row_pos[2] = {p0 + warp * 16 + g, p0 + warp * 16 + g + 8};  // positions of this thread's two rows
 
   for (int trip = 0; trip < n_trips; ++trip) {
@@ -155,8 +163,15 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloa
       }
     }
 
-    // mask by selection where the page crosses a query's position or its window's start
     const int key0 = kb * kRows;
+    if (slopes) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          sc[i][j] = fmaf(-slope_raw, (float)(row_pos[j >> 1] - (key0 + i * 8 + c2 + (j & 1))), sc[i][j]);
+    }
+    // mask by selection where the page crosses a query's position or its window's start
     const bool need_mask = key0 + kRows - 1 > p0 + warp * 16 || (window > 0 && key0 < p_last - window + 1);  // (kept pages too)
     if (need_mask) {
 #pragma unroll
@@ -249,7 +264,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloa
 template <int HD>
 int launch(const void* qkv, const void* kc, const void* vc, void* out, const int* seq_slot, const int* seq_start,
            const int* seq_new, const int* cu_new, const int* pages, int max_blocks, int n_seqs, int max_new,
-           int n_heads, int kv_heads, float scale, int window, int keep_first, cudaStream_t stream) {
+           int n_heads, int kv_heads, float scale, int window, int keep_first, const float* slopes, const float* sinks,
+           cudaStream_t stream) {
   const int smem = 5 * kRows * (HD + 8) * (int)sizeof(__nv_bfloat16);
   static bool configured = false;  // per instantiation
   if (!configured) {
@@ -260,17 +276,28 @@ int launch(const void* qkv, const void* kc, const void* vc, void* out, const int
   dim3 grid((max_new + kRows - 1) / kRows, n_heads, n_seqs);
   attention_prefill_kernel<HD><<<grid, kThreads, smem, stream>>>(
       (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, seq_slot,
-      seq_start, seq_new, cu_new, pages, max_blocks, n_heads, kv_heads, scale * 1.4426950408889634f, window, keep_first);
+      seq_start, seq_new, cu_new, pages, max_blocks, n_heads, kv_heads, scale * 1.4426950408889634f, window, keep_first, slopes,
+      sinks);
   EMBER_LAUNCH_OK("attention_prefill");
   return 0;
 }
 
 }  // namespace
 
+EMBER_API int ember_attention_prefill_biased(const void* qkv, const void* kc, const void* vc, void* out, const int* seq_slot,
+                                             const int* seq_start, const int* seq_new, const int* cu_new, const int* pages,
+                                             int max_blocks, int n_seqs, int max_new, int n_heads, int kv_heads, int hd,
+                                             float scale, int window, int keep_first, const float* slopes, const float* sinks,
+                                             cudaStream_t stream);
+
+// The same with the first `keep_first` positions of every sequence visible beside the window.
 EMBER_API int ember_attention_prefill_kept(const void* qkv, const void* kc, const void* vc, void* out, const int* seq_slot,
                                            const int* seq_start, const int* seq_new, const int* cu_new, const int* pages,
                                            int max_blocks, int n_seqs, int max_new, int n_heads, int kv_heads, int hd,
-                                           float scale, int window, int keep_first, cudaStream_t stream);
+                                           float scale, int window, int keep_first, cudaStream_t stream) {
+  return ember_attention_prefill_biased(qkv, kc, vc, out, seq_slot, seq_start, seq_new, cu_new, pages, max_blocks, n_seqs,
+                                        max_new, n_heads, kv_heads, hd, scale, window, keep_first, nullptr, nullptr, stream);
+}
 
 // Returns 0 on success, 1 on an error, 2 if this head size has no tensor-core instantiation (the
 // caller then takes the plain kernel).
@@ -282,11 +309,13 @@ EMBER_API int ember_attention_prefill(const void* qkv, const void* kc, const voi
                                       max_new, n_heads, kv_heads, hd, scale, window, 0, stream);
 }
 
-// The same with the first `keep_first` positions of every sequence visible beside the window.
-EMBER_API int ember_attention_prefill_kept(const void* qkv, const void* kc, const void* vc, void* out, const int* seq_slot,
-                                           const int* seq_start, const int* seq_new, const int* cu_new, const int* pages,
-                                           int max_blocks, int n_seqs, int max_new, int n_heads, int kv_heads, int hd,
-                                           float scale, int window, int keep_first, cudaStream_t stream) {
+// The same with a distance penalty (slopes: float32 per query head, or null) and a sink in the softmax's denominator
+// (sinks: float32 per query head, or null).
+EMBER_API int ember_attention_prefill_biased(const void* qkv, const void* kc, const void* vc, void* out, const int* seq_slot,
+                                             const int* seq_start, const int* seq_new, const int* cu_new, const int* pages,
+                                             int max_blocks, int n_seqs, int max_new, int n_heads, int kv_heads, int hd,
+                                             float scale, int window, int keep_first, const float* slopes, const float* sinks,
+                                             cudaStream_t stream) {
   EMBER_CHECK(n_seqs > 0 && max_new > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0, "attention_prefill: bad sizes");
   EMBER_CHECK(n_heads % kv_heads == 0, "attention_prefill: %d heads are not a multiple of %d key/value heads", n_heads,
               kv_heads);
@@ -299,7 +328,7 @@ EMBER_API int ember_attention_prefill_kept(const void* qkv, const void* kc, cons
 #define EMBER_PREFILL(HD)                                                                                           \
   case HD:                                                                                                          \
     return launch<HD>(qkv, kc, vc, out, seq_slot, seq_start, seq_new, cu_new, pages, max_blocks, n_seqs, max_new,   \
-                      n_heads, kv_heads, scale, window, keep_first, stream)
+                      n_heads, kv_heads, scale, window, keep_first, slopes, sinks, stream)
   switch (hd) {
     EMBER_PREFILL(16);
     EMBER_PREFILL(32);

@@ -99,6 +99,11 @@ _SIGNATURES = {
                          _c_int, _c_void],
     "ember_attention_plain_biased": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
                                      _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void],
+    "ember_attention_prefill_biased": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
+                                       _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void, _c_void,
+                                       _c_void],
+    "ember_attention_decode_biased": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
+                                      _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void],
     "ember_add_branches": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_float, _c_void],
     "ember_qkv_norm": [_c_void, ctypes.c_longlong, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
                        _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_void],
@@ -690,26 +695,24 @@ class CudaOps:
                        plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), pages.data_ptr(), plan.max_blocks, plan.T,
                        n_heads, kv_heads, hd, vd, _code(qkv.dtype))
         fast = self.attention_kept_fast and qkv.dtype == torch.bfloat16
-        biased = slopes is not None or sinks is not None
-        if biased:
-            fast = False
         if fast and plan.all_single and plan.T == plan.n:
             # one token each: the visible keys in chunks of 128, a block a chunk and key/value head, then the merge
             max_keys = min(keep_first + window, plan.max_end) if window > 0 else plan.max_end
             scratch = torch.empty(self.lib.ember_attention_decode_kept_scratch(plan.T, n_heads, vd, max_keys),
                                   dtype=torch.float32, device=qkv.device)
-            rc = self._call("ember_attention_decode_kept", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+            rc = self._call("ember_attention_decode_biased", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
                             out.data_ptr(), scratch.data_ptr(), plan.positions.data_ptr(), plan.seq_slot.data_ptr(),
                             pages.data_ptr(), plan.max_blocks, plan.T, n_heads, kv_heads, hd, vd, float(scale), int(window),
-                            keep_first, int(max_keys), allow=(2,))
+                            keep_first, int(max_keys), self._ptr(slopes), self._ptr(sinks), allow=(2,))
             if rc == 0:
                 self.launches += 1      # (the merge)
                 return out
         if fast and vd == hd and hd % 16 == 0 and hd <= 128 and scale > 0 and not plan.all_single:
-            rc = self._call("ember_attention_prefill_kept", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+            rc = self._call("ember_attention_prefill_biased", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
                             out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.seq_new.data_ptr(),
                             plan.cu_new.data_ptr(), pages.data_ptr(), plan.max_blocks, plan.n, plan.max_new, n_heads,
-                            kv_heads, hd, float(scale), int(window), keep_first, allow=(2,))
+                            kv_heads, hd, float(scale), int(window), keep_first, self._ptr(slopes), self._ptr(sinks),
+                            allow=(2,))
             if rc == 0:
                 return out
         self._call("ember_attention_plain_biased", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), out.data_ptr(),
