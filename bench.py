@@ -232,6 +232,34 @@ MUZOZEN_SIZES = {
 }
 
 
+SOSUTAR_SIZES = {
+    # mLSTM: heads / key size / value size (heads x value size = the width); minGRU: its state's width
+    "small": dict(m_heads=8, m_dim=64, m_vdim=128, gru=2048),
+    "medium": dict(m_heads=8, m_dim=128, m_vdim=256, gru=4096),
+}
+
+
+def sosutar_config(size: str):
+    """A Sosutar of the width, layer count, attention heads, window, dense inner size and vocabulary of `DESIGN_SIZES[size]`:
+    an mLSTM layer without a feed-forward, layers of attention beside a minGRU with a feed-forward, and a last mLSTM layer
+    that runs with the first one's tensors."""
+    z, m = DESIGN_SIZES[size], SOSUTAR_SIZES[size]
+    left = {"dim": z["dim"], "vdim": z["dim"], "heads": z["heads"], "kv_heads": z["kv_heads"], "scale": z["dim"] ** -0.5,
+            "mask": {"size": z["window"]}, "q_temp": {"coef": 0.1, "every": 256}}
+    mlstm = {"type": "mlstm", "mixer": {"heads": m["m_heads"], "dim": m["m_dim"], "vdim": m["m_vdim"], "gate_cap": 15.0}, "mlp": None}
+    layers = []
+    for i in range(z["layers"]):
+        if i == 0:
+            layers.append(dict(mlstm))
+        elif i == z["layers"] - 1 and i > 1:
+            layers.append(dict(mlstm, weights_of=0))
+        else:
+            layers.append({"type": "parallel", "mixer": {"left": dict(left), "right": {"width": m["gru"]}},
+                           "mlp": {"kind": "dense", "ff": z["ff"]}})
+    return {"architecture": "Sosutar", "vocab": z["vocab"], "width": z["width"], "max_positions": 8192, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 8.0}, "logit_scale": 0.5, "layers": layers}
+
+
 def muzozen_config(size: str):
     """A Muzozen of the width, layer count, dense inner size and vocabulary of `DESIGN_SIZES[size]`: attention over cached
     rows, a delta-rule layer, an attention layer that reads the first layer's rows, and so on in turn."""
@@ -255,6 +283,8 @@ def design_configs(size: str, design: str = "nipolorn"):
     its configuration in front of the two."""
     if design == "muzozen":
         return (muzozen_config(size),) + design_configs(size)
+    if design == "sosutar":
+        return (sosutar_config(size),) + design_configs(size)
     z = DESIGN_SIZES[size]
     left = {"dim": z["dim"], "vdim": z["dim"], "heads": z["heads"], "kv_heads": z["kv_heads"], "scale": z["dim"] ** -0.5,
             "mask": {"size": z["window"], "keep_first": z["keep"]}}
@@ -388,7 +418,7 @@ def main() -> int:
                     help="time one bfloat16 product on every kernel that takes it, instead of the benchmark")
     ap.add_argument("--act", default=None, choices=[None, "gelu_tanh", "gelu_erf"], help="with --linear: the epilogue's activation")
     ap.add_argument("--residual", action="store_true", help="with --linear: add a float32 residual (the output is float32 then)")
-    ap.add_argument("--design", default=None, choices=["nipolorn", "muzozen"],
+    ap.add_argument("--design", default=None, choices=["nipolorn", "muzozen", "sosutar"],
                     help="instead of the benchmark: prefill and decode throughput of this design beside a GPT-2 of equal size "
                          "(muzozen: beside a Nipolorn and a GPT-2 of equal size)")
     ap.add_argument("--design-size", default="medium", choices=sorted(DESIGN_SIZES), help="with --design: the layers' sizes")

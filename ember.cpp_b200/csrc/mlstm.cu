@@ -16,6 +16,13 @@
 // is independent of the others, so a token's result depends on its sequence alone, never on the batch
 // or the step's cut.  A sequence that starts at position 0 starts from zeros whatever its slot's state
 // holds; sequences of slot -1 are padding: their rows are zero and no state is touched.
+//
+// A long sequence is cut into pieces that are walked side by side.  The recurrence is linear in (S, n) once
+// the gates are known, and the maximum is associative: a piece walked from nothing (S = 0, n = 0, m = -inf)
+// ends in (S', n', m') and the sum F of its log forget gates, and a state (S, n, m) in front of it becomes
+// m'' = max(F + m, m'), S'' = exp(F + m - m'') S + exp(m' - m'') S' (n likewise).  So: a first walk of every
+// piece from nothing, a small kernel that makes every piece's start state from those in order, and a second
+// walk of every piece from its start state, which writes the results.
 #include "common.cuh"
 
 namespace {
@@ -47,7 +54,7 @@ __global__ void mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, i
                                   const float* __restrict__ gates, float* __restrict__ S_state, float* __restrict__ n_state,
                                   float* __restrict__ m_state, float* __restrict__ out, const int* __restrict__ seq_slot,
                                   const int* __restrict__ seq_start, const int* __restrict__ cu_new, int heads, int dim,
-                                  int vdim, float floor_) {
+                                  int vdim, float floor_, int piece, int pieces, int phase, float* __restrict__ scratch) {
   extern __shared__ float smem[];
   const int cols = blockDim.x - 32;
   float* ks = smem;                         // [kStage][DMAX]
@@ -56,23 +63,31 @@ __global__ void mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, i
   float* keep = vs + kStage * cols;         // [kStage] exp(f + m_before - m)
   float* take = keep + kStage;              // [kStage] exp(i - m)
   float* den = take + kStage;               // [kStage] exp(-m), then the denominator
-  const int s = blockIdx.x, h = blockIdx.y;
+  // phase 0: the whole walk (one piece).  phase 1: a piece from nothing, its end left in scratch.  phase 2: a piece from
+  // the start state that the carry left in scratch.
+  const int s = blockIdx.x / pieces, pc = blockIdx.x % pieces, h = blockIdx.y;
   const bool column = (int)threadIdx.x < cols;
   const int j = blockIdx.z * cols + threadIdx.x;
   const bool live = column && j < vdim;
   const int lane = threadIdx.x & 31;
-  const int t0 = cu_new[s], n = cu_new[s + 1] - t0;
+  const int seq_n = cu_new[s + 1] - cu_new[s];
+  const int lo = pc * piece, hi = min(seq_n, lo + piece);
+  if (lo >= seq_n) return;
+  const int t0 = cu_new[s] + lo, n = hi - lo;
   const int slot = seq_slot[s];
   const int inner = heads * vdim;
   if (slot < 0) {
-    if (live)
+    if (live && phase != 1)
       for (int i = 0; i < n; ++i) out[(size_t)(t0 + i) * inner + (size_t)h * vdim + j] = 0.f;
     return;
   }
-  const bool carried = seq_start[s] > 0;
+  const bool carried = phase == 2 || (phase == 0 && seq_start[s] > 0);
   const float q_scale = rsqrtf((float)dim);
-  float* col = S_state + ((size_t)slot * heads + h) * dim * vdim + j;
-  float* nrow = n_state + ((size_t)slot * heads + h) * dim;
+  // where this walk starts from and where it leaves its end: the slot's rows, or the piece's place in scratch
+  float* mine = phase == 0 ? nullptr : scratch + ((size_t)blockIdx.x * heads + h) * ((size_t)dim * vdim + dim + 3);
+  float* col = (phase == 0 ? S_state + ((size_t)slot * heads + h) * dim * vdim : mine) + j;
+  float* nrow = phase == 0 ? n_state + ((size_t)slot * heads + h) * dim : mine + (size_t)dim * vdim;
+  float* mval = phase == 0 ? m_state + (size_t)slot * heads + h : mine + (size_t)dim * vdim + dim + (phase == 2 ? 2 : 0);
   float S[DMAX];              // a column thread: S[:, j]; a lane of the normaliser's warp: n[lane + 32 r] in S[r]
   if (column) {
 #pragma unroll
@@ -84,7 +99,8 @@ __global__ void mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, i
       S[r] = (carried && d < dim) ? nrow[d] : 0.f;
     }
   }
-  float m = carried ? m_state[(size_t)slot * heads + h] : 0.f;   // walked by the normaliser's first lane
+  float m = carried ? *mval : (phase == 1 ? -INFINITY : 0.f);   // walked by the normaliser's first lane
+  float F = 0.f;                                                 // (phase 1) the sum of the piece's log forget gates
 
   for (int c0 = 0; c0 < n; c0 += kStage) {
     const int cn = min(kStage, n - c0);
@@ -107,10 +123,24 @@ __global__ void mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, i
         take[i] = expf(li - m_new);
         den[i] = expf(-m_new);
         m = m_new;
+        F += lf;
       }
     }
     __syncthreads();
-    if (column) {
+    if (column && phase == 1) {      // no results: the memory alone
+      for (int i = 0; i < cn; ++i) {
+        const float* k = ks + i * DMAX;
+        const float a = keep[i], b = take[i] * vs[i * cols + threadIdx.x];
+#pragma unroll
+        for (int d = 0; d < DMAX; d += 4) {
+          const float4 kv = *reinterpret_cast<const float4*>(k + d);
+          S[d] = fmaf(a, S[d], b * kv.x);
+          S[d + 1] = fmaf(a, S[d + 1], b * kv.y);
+          S[d + 2] = fmaf(a, S[d + 2], b * kv.z);
+          S[d + 3] = fmaf(a, S[d + 3], b * kv.w);
+        }
+      }
+    } else if (column) {
       for (int i = 0; i < cn; ++i) {
         const float* k = ks + i * DMAX;
         const float* q = qs + i * DMAX;
@@ -146,9 +176,16 @@ __global__ void mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, i
       }
     }
     __syncthreads();
-    if (live)
+    if (live && phase != 1)
       for (int i = 0; i < cn; ++i)
         out[(size_t)(t0 + c0 + i) * inner + (size_t)h * vdim + j] = vs[i * cols + threadIdx.x] / den[i];
+  }
+  // the end: into the piece's place (phase 1), or into the slot's rows by the walk that reaches the sequence's end
+  if (phase == 2) {
+    if (hi < seq_n) return;
+    col = S_state + ((size_t)slot * heads + h) * dim * vdim + j;
+    nrow = n_state + ((size_t)slot * heads + h) * dim;
+    mval = m_state + (size_t)slot * heads + h;
   }
   if (live) {
 #pragma unroll
@@ -161,14 +198,47 @@ __global__ void mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, i
       const int d = lane + 32 * r;
       if (d < dim) nrow[d] = S[r];
     }
-    if (lane == 0) m_state[(size_t)slot * heads + h] = m;
+    if (lane == 0) {
+      *mval = m;
+      if (phase == 1) mval[1] = F;
+    }
+  }
+}
+
+// grid (sequences, heads, blocks over the dim * vdim + dim values of S and n): every piece's place in scratch, which holds
+// the piece's end from nothing (S', n', m', F, -), gets the state in front of the piece (S, n, -, -, m) instead.
+__global__ void mlstm_carry_kernel(float* __restrict__ scratch, const float* __restrict__ S_state, const float* __restrict__ n_state,
+                                   const float* __restrict__ m_state, const int* __restrict__ seq_slot,
+                                   const int* __restrict__ seq_start, const int* __restrict__ cu_new, int heads, int dim, int vdim,
+                                   int piece, int pieces) {
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int e = blockIdx.z * blockDim.x + threadIdx.x;
+  const int values = dim * vdim + dim;
+  const int slot = seq_slot[s];
+  if (slot < 0 || e >= values) return;
+  const int seq_n = cu_new[s + 1] - cu_new[s];
+  const bool carried = seq_start[s] > 0;
+  float cur = 0.f, m = 0.f;
+  if (carried) {
+    cur = e < dim * vdim ? S_state[((size_t)slot * heads + h) * dim * vdim + e] : n_state[((size_t)slot * heads + h) * dim + e - dim * vdim];
+    m = m_state[(size_t)slot * heads + h];
+  }
+  for (int p = 0; p < pieces && p * piece < seq_n; ++p) {
+    float* mine = scratch + (((size_t)s * pieces + p) * heads + h) * ((size_t)values + 3);
+    const float m_loc = mine[values], F = mine[values + 1];
+    const float m_new = fmaxf(F + m, m_loc);
+    const float next = expf(F + m - m_new) * cur + expf(m_loc - m_new) * mine[e];
+    mine[e] = cur;
+    if (e == 0) mine[values + 2] = m;
+    cur = next;
+    m = m_new;
   }
 }
 
 template <typename T, int DMAX>
 cudaError_t launch_scan(const void* qkv, long long stride, int q_col, int k_col, int v_col, const float* gates, float* S, float* n,
                         float* m, float* out, const int* seq_slot, const int* seq_start, const int* cu_new, int n_seqs, int heads,
-                        int dim, int vdim, float floor_, cudaStream_t stream) {
+                        int dim, int vdim, float floor_, int piece, int pieces, float* scratch, cudaStream_t stream) {
   // columns a block: all of a head's where they are few, so that the normaliser is walked once
   const int cols = vdim <= 128 ? (vdim + 31) / 32 * 32 : 64;
   const int tiles = (vdim + cols - 1) / cols;
@@ -178,16 +248,28 @@ cudaError_t launch_scan(const void* qkv, long long stride, int q_col, int k_col,
     const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  return launch_plain(kernel, dim3(n_seqs, heads, tiles), dim3(cols + 32), smem, stream, (const T*)qkv, stride, q_col, k_col,
-                      v_col, gates, S, n, m, out, seq_slot, seq_start, cu_new, heads, dim, vdim, floor_);
+  cudaError_t e = cudaSuccess;
+  for (int phase = pieces > 1 ? 1 : 0; phase <= (pieces > 1 ? 2 : 0) && e == cudaSuccess; ++phase) {
+    e = launch_plain(kernel, dim3(n_seqs * pieces, heads, tiles), dim3(cols + 32), smem, stream, (const T*)qkv, stride, q_col, k_col,
+                     v_col, gates, S, n, m, out, seq_slot, seq_start, cu_new, heads, dim, vdim, floor_, piece, pieces, phase, scratch);
+    if (phase == 1 && e == cudaSuccess) {
+      const int values = dim * vdim + dim;
+      e = launch_plain(mlstm_carry_kernel, dim3(n_seqs, heads, (values + 255) / 256), dim3(256), 0, stream, scratch,
+                       (const float*)S, (const float*)n, (const float*)m, seq_slot, seq_start, cu_new, heads, dim, vdim, piece,
+                       pieces);
+    }
+  }
+  return e;
 }
 
 template <typename T>
 cudaError_t launch_scan_any(int dim, const void* qkv, long long stride, int q_col, int k_col, int v_col, const float* gates, float* S,
                             float* n, float* m, float* out, const int* seq_slot, const int* seq_start, const int* cu_new,
-                            int n_seqs, int heads, int vdim, float floor_, cudaStream_t stream) {
-#define EMBER_SCAN(D) \
-  launch_scan<T, D>(qkv, stride, q_col, k_col, v_col, gates, S, n, m, out, seq_slot, seq_start, cu_new, n_seqs, heads, dim, vdim, floor_, stream)
+                            int n_seqs, int heads, int vdim, float floor_, int piece, int pieces, float* scratch,
+                            cudaStream_t stream) {
+#define EMBER_SCAN(D)                                                                                                            \
+  launch_scan<T, D>(qkv, stride, q_col, k_col, v_col, gates, S, n, m, out, seq_slot, seq_start, cu_new, n_seqs, heads, dim, vdim, \
+                    floor_, piece, pieces, scratch, stream)
   if (dim <= 32) return EMBER_SCAN(32);
   if (dim <= 64) return EMBER_SCAN(64);
   if (dim <= 128) return EMBER_SCAN(128);
@@ -217,20 +299,28 @@ EMBER_API int ember_mlstm_gates(const void* h, const void* w, const float* bias,
 
 // qkv: rows of `stride` values holding q (heads x dim) from q_col, k from k_col, v (heads x vdim) from v_col; gates as
 // ember_mlstm_gates leaves them; S [slots, heads, dim, vdim], n [slots, heads, dim], m [slots, heads] float32 (advanced);
-// out float32 [T, heads * vdim].
+// out float32 [T, heads * vdim].  pieces 1: one walk of every sequence; more (with scratch of ember_mlstm_scan_scratch floats):
+// pieces of `piece` tokens side by side.
+EMBER_API size_t ember_mlstm_scan_scratch(int n_seqs, int pieces, int heads, int dim, int vdim) {
+  return (size_t)n_seqs * pieces * heads * ((size_t)dim * vdim + dim + 3);
+}
+
 EMBER_API int ember_mlstm_scan(const void* qkv, long long stride, int q_col, int k_col, int v_col, const float* gates, float* S,
                                float* n, float* m, float* out, const int* seq_slot, const int* seq_start, const int* cu_new,
-                               int n_seqs, int heads, int dim, int vdim, float floor_, int dtype, cudaStream_t stream) {
-  EMBER_CHECK(n_seqs > 0 && heads > 0 && vdim > 0, "mlstm_scan: bad sizes");
+                               int n_seqs, int heads, int dim, int vdim, float floor_, int piece, int pieces, float* scratch,
+                               int dtype, cudaStream_t stream) {
+  EMBER_CHECK(n_seqs > 0 && heads > 0 && vdim > 0 && piece >= 1 && pieces >= 1, "mlstm_scan: bad sizes");
+  EMBER_CHECK(pieces == 1 || scratch != nullptr, "mlstm_scan: pieces side by side need scratch");
+  EMBER_CHECK((long long)n_seqs * pieces <= 2147483647LL, "mlstm_scan: %d sequences x %d pieces exceed one launch", n_seqs, pieces);
   EMBER_CHECK(dim >= 1 && dim <= 256, "mlstm_scan: a key size of %d is not in [1, 256]", dim);
   EMBER_CHECK(heads <= 65535, "mlstm_scan: %d heads exceed one launch", heads);
   cudaError_t e;
   if (dtype == EMBER_F32)
     e = launch_scan_any<float>(dim, qkv, stride, q_col, k_col, v_col, gates, S, n, m, out, seq_slot, seq_start, cu_new, n_seqs,
-                               heads, vdim, floor_, stream);
+                               heads, vdim, floor_, piece, pieces, scratch, stream);
   else if (dtype == EMBER_BF16)
     e = launch_scan_any<__nv_bfloat16>(dim, qkv, stride, q_col, k_col, v_col, gates, S, n, m, out, seq_slot, seq_start, cu_new,
-                                       n_seqs, heads, vdim, floor_, stream);
+                                       n_seqs, heads, vdim, floor_, piece, pieces, scratch, stream);
   else
     return ember_fail("mlstm_scan: element type %d", dtype);
   if (e != cudaSuccess) return ember_fail("mlstm_scan: %s", cudaGetErrorString(e));

@@ -110,7 +110,7 @@ _SIGNATURES = {
     "ember_gate_mul": [_c_void, _c_void, ctypes.c_longlong, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_mlstm_gates": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ember_mlstm_scan": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
-                         _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
+                         _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void, _c_int, _c_void],
     "ember_mingru": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
                      _c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_int, _c_void],
     "ember_sample": [_c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_float, _c_u64, _c_void, _c_void, _c_u64, _c_void],
@@ -178,6 +178,8 @@ def load_library() -> ctypes.CDLL:
     lib.ember_delta_rule_scratch.restype = _c_size
     lib.ember_attention_decode_kept_scratch.argtypes = [_c_int] * 4
     lib.ember_attention_decode_kept_scratch.restype = _c_size
+    lib.ember_mlstm_scan_scratch.argtypes = [_c_int] * 5
+    lib.ember_mlstm_scan_scratch.restype = _c_size
     lib.ember_mingru_scratch.argtypes = [_c_int] * 3
     lib.ember_mingru_scratch.restype = _c_size
     for name in ("ember_tc_status", "ember_linear_decode_status", "ember_attention_decode_status",
@@ -941,7 +943,9 @@ class CudaOps:
                    bias.data_ptr(), gates.data_ptr(), T, heads, width, float(cap), _code(h.dtype))
         return gates
 
-    def mlstm_scan(self, proj, q_col, k_col, v_col, gates, state, plan, heads, dim, vdim, floor):
+    MLSTM_PIECE = 128       # tokens of a piece when a long sequence's recurrence is walked in pieces side by side
+
+    def mlstm_scan(self, proj, q_col, k_col, v_col, gates, state, plan, heads, dim, vdim, floor, pieces=None):
         """The recurrence of parts/mlstm.py over the step's sequences: q, k (heads x dim) and v (heads x vdim) are
         columns of `proj`; state: {"S": [slots, heads, dim, vdim], "n": [slots, heads, dim], "m": [slots, heads]}
         float32 (advanced); float32 [T, heads * vdim]."""
@@ -954,9 +958,20 @@ class CudaOps:
         if max(q_col, k_col) + heads * dim > proj.shape[1] or v_col + heads * vdim > proj.shape[1]:
             raise KernelError("mlstm_scan: the columns of q, k and v do not fit the rows")
         out = torch.empty((plan.T, heads * vdim), dtype=torch.float32, device=proj.device)
+        longest = max(int(plan.max_new), 1)
+        if pieces is None:      # (a second walk pays from four pieces on)
+            pieces = -(-longest // self.MLSTM_PIECE) if longest >= 4 * self.MLSTM_PIECE else 1
+        piece = -(-longest // pieces)
+        scratch = None
+        if pieces > 1:
+            scratch = torch.empty(self.lib.ember_mlstm_scan_scratch(plan.n, pieces, heads, dim, vdim), dtype=torch.float32,
+                                  device=proj.device)
         self._call("ember_mlstm_scan", proj.data_ptr(), proj.stride(0), int(q_col), int(k_col), int(v_col), gates.data_ptr(),
                    S.data_ptr(), n.data_ptr(), m.data_ptr(), out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(),
-                   plan.cu_new.data_ptr(), plan.n, heads, dim, vdim, float(floor), _code(proj.dtype))
+                   plan.cu_new.data_ptr(), plan.n, heads, dim, vdim, float(floor), piece, pieces, self._ptr(scratch),
+                   _code(proj.dtype))
+        if pieces > 1:
+            self.launches += 2
         return out
 
     MINGRU_PIECE = 128      # tokens of a piece when a long sequence's recurrence is walked in pieces side by side

@@ -74,6 +74,42 @@ def ids(seed: int, vocab: int, n: int) -> list:
     return np.random.default_rng(seed).integers(0, vocab, n).tolist()
 
 
+def steady_tokens(m) -> list:
+    """Tokens that a test sequence may begin with.  At a sequence's first position the matrix memory holds one term, so
+    a head's read-out is its value times the sign of k . q (the head's norm takes the size away); for a token whose
+    k . q happens to lie near zero in some head of some layer, a rounding of q or k in bfloat16 decides that sign, and no
+    tolerance on the logits is meaningful.  These are the tokens whose |k . q| / (|k| |q|) is above 0.1 in every
+    head of every such layer, by the plain model `m`."""
+    import plain_sosutar as P
+    cfg, eps = m.cfg, m.cfg["norm"]["eps"]
+    steady = []
+    for tok in range(cfg["vocab"]):
+        x = m.w["embed"][[tok]] * cfg["embedding"]["scale"] + m.w["pos"][:1]
+        worst = 1.0
+        for i, layer in enumerate(cfg["layers"]):
+            if layer["type"] == "mlstm":
+                p, c = f"l{layer.get('weights_of', i)}.mix.", layer["mixer"]
+                h = P.rms_norm(x, m.w[p[:-4] + "norm1"], eps)
+                q, k = ((h @ m.w[p + n].T).reshape(c["heads"], c["dim"]) for n in ("q", "k"))
+                worst = min(worst, (np.abs((q * k).sum(-1)) / (np.linalg.norm(q, axis=1) * np.linalg.norm(k, axis=1))).min())
+            x = P.layer(m, i, x)
+        if worst > 0.1:
+            steady.append(tok)
+    return steady
+
+
+def sequences(m, seed: int, lengths) -> list:
+    """Random sequences of the given lengths for the plain model `m`, each beginning with a steady token."""
+    steady = steady_tokens(m) if not hasattr(m, "_steady") else m._steady
+    m._steady = steady
+    out = []
+    for i, n in enumerate(lengths):
+        seq = ids(seed + i, m.cfg["vocab"], n)
+        seq[0] = steady[(seed + i) % len(steady)]
+        out.append(seq)
+    return out
+
+
 def row_error(got, ref) -> float:
     """Worst row of rms(delta - mean(delta)) / rms(ref - mean(ref))."""
     got, ref = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)

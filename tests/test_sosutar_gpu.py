@@ -188,7 +188,9 @@ def test_the_matrix_memory_keeps_a_token_from_far_back(ops):
     proj[20, dim:2 * dim] = 3.0
     proj[20, 2 * dim:2 * dim + vdim] = 50.0
     proj[620, :dim] = 3.0
-    gates = torch.stack([torch.full((T,), -6.0), torch.full((T,), -1e-4)], 1)
+    # (a log forget gate that is a power of two: the running maximum then falls by exact steps in float32, where a value
+    # like 1e-4 would be rounded the same way 600 times over and the maximum would drift by 6e-5)
+    gates = torch.stack([torch.full((T,), -6.0), torch.full((T,), -2.0 ** -13)], 1)
     gates[20, 0] = 4.0
     state = {"S": torch.zeros(1, 1, dim, vdim).cuda(), "n": torch.zeros(1, 1, dim).cuda(), "m": torch.zeros(1, 1).cuda()}
     got = ops.mlstm_scan(proj.cuda(), 0, dim, 2 * dim, gates.cuda(), state, plan_of([(0, 0, T)]), 1, dim, vdim, 1e-6)
@@ -196,6 +198,38 @@ def test_the_matrix_memory_keeps_a_token_from_far_back(ops):
     want = P.mlstm_recurrence(x[:, :dim] * dim ** -0.5, x[:, dim:2 * dim], x[:, 2 * dim:2 * dim + vdim], f64(gates[:, 0]), f64(gates[:, 1]))
     assert want[620].min() > 40.0
     close(got, want, 3e-5)
+
+
+@pytest.mark.parametrize("pieces", [1, 2, 5])
+@pytest.mark.parametrize("heads, dim, vdim", [(2, 16, 24), (1, 40, 136)])
+def test_mlstm_in_pieces_side_by_side_equals_one_walk(ops, pieces, heads, dim, vdim):
+    """Two sequences of unequal length, one of them on top of a carried state (its running maximum not zero); the shorter
+    one ends before the last pieces begin."""
+    lengths = (300, 70)
+    qk, inner = heads * dim, heads * vdim
+    rows = rnd(1, sum(lengths), 2 * qk + inner, scale=0.7)
+    gates = torch.cat([rnd(2, sum(lengths), heads, scale=2.0) - 1.0, -torch.nn.functional.softplus(rnd(3, sum(lengths), heads) - 2.0)], 1)
+    first = {"S": rnd(4, 2, heads, dim, vdim), "n": rnd(5, 2, heads, dim), "m": rnd(6, 2, heads).abs() + 0.5}
+    state = {k: v.clone().cuda() for k, v in first.items()}
+    plan = plan_of([(0, 0, lengths[0]), (1, 9, lengths[1])])
+    got = f64(ops.mlstm_scan(rows.cuda(), 0, qk, 2 * qk, gates.cuda(), state, plan, heads, dim, vdim, 1e-6, pieces=pieces))
+    x, g, at = f64(rows), f64(gates), 0
+    for i, n in enumerate(lengths):
+        for a in range(heads):
+            S = np.zeros((dim, vdim)) if i == 0 else f64(first["S"][1, a])
+            nn = np.zeros(dim) if i == 0 else f64(first["n"][1, a])
+            m = 0.0 if i == 0 else float(first["m"][1, a])
+            for t in range(at, at + n):
+                q, k = x[t, a * dim:(a + 1) * dim] * dim ** -0.5, x[t, qk + a * dim:qk + (a + 1) * dim]
+                v = x[t, 2 * qk + a * vdim:2 * qk + (a + 1) * vdim]
+                m_new = max(g[t, heads + a] + m, g[t, a])
+                keep, take = math.exp(g[t, heads + a] + m - m_new), math.exp(g[t, a] - m_new)
+                S, nn, m = keep * S + take * np.outer(k, v), keep * nn + take * k, m_new
+                want = (S.T @ q) / (max(abs(nn @ q), math.exp(-m)) + 1e-6)
+                assert np.abs(got[t, a * vdim:(a + 1) * vdim] - want).max() < 3e-5 * max(1.0, np.abs(want).max()), (i, a, t)
+            assert np.abs(f64(state["S"][i, a]) - S).max() < 3e-5 * max(1.0, np.abs(S).max())
+            assert np.abs(f64(state["n"][i, a]) - nn).max() < 3e-5 * max(1.0, np.abs(nn).max()) and abs(float(state["m"][i, a]) - m) < 1e-5
+        at += n
 
 
 # ------------------------------------------------------------------------------ minGRU
@@ -347,7 +381,7 @@ def test_one_marked_key_is_seen_exactly_inside_the_window_and_pays_for_its_dista
                     assert (value > 5.0) if seen else (abs(value) < 1e-2), (marked, i, a, seen, value)
         near, far = marked + 1, marked + window - 1
         if far < T:
-            assert got[near, 0] > 95.0 and got[far, 0] < 30.0          # e^(7 - 0.05 * 89) against some 90 others and the sink
+            assert got[near, 0] > 95.0 and got[far, 0] < 50.0          # e^(7 - 0.05 * 89) against up to 90 others and the sink
             assert got[near, hd] > 95.0 and got[far, hd] > 85.0        # e^7 against some 90 others
 
 
@@ -374,7 +408,7 @@ def engines(folders):
 def test_prompts_decoding_portions_and_batches_equal_the_plain_model(engines, plains, name, dtype):
     eng, m = engines[(name, dtype)], plains[name]
     vocab = m.cfg["vocab"]
-    seqs = [U.ids(10 + i, vocab, n) for i, n in enumerate((200, 1, 40, 97, 2))]
+    seqs = U.sequences(m, 10, (200, 1, 40, 97, 2))
     refs = [P.forward(m, s) for s in seqs]
     for prompts in ([len(s) for s in seqs], [150, 1, 1, 30, 1]):
         got, _ = run_batch(eng, seqs, prompts)
@@ -409,7 +443,7 @@ def test_long_decoding_past_the_window_with_slots_used_again(folders, plains, dt
     slots, state rows and pages that the batch before it left (filled with NaN in between)."""
     eng, m = E.Engine.from_folder(folders["sos_a"], dtype=dtype, max_tokens=384), plains["sos_a"]
     for round_ in range(2):
-        seqs = [U.ids(200 * round_ + i, 300, n) for i, n in enumerate((330, 90))]
+        seqs = U.sequences(m, 200 * round_, (330, 90))
         got, slots = run_batch(eng, seqs, [3, 70])
         assert sorted(slots) == [0, 1]
         assert max(U.row_error(g, P.forward(m, s)) for g, s in zip(got, seqs)) < U.TOL[dtype]
@@ -425,7 +459,7 @@ def test_long_decoding_past_the_window_with_slots_used_again(folders, plains, dt
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_a_long_prompt_takes_the_recurrences_in_pieces(folders, plains, dtype):
     eng, m = E.Engine.from_folder(folders["sos_b"], dtype=dtype, max_tokens=1024), plains["sos_b"]
-    seq = U.ids(77, 200, 512)
+    seq = U.sequences(m, 77, (512,))[0]
     got, _ = run_batch(eng, [seq], [511])
     assert U.row_error(got[0], P.forward(m, seq)) < U.TOL[dtype]
 
@@ -446,7 +480,7 @@ def test_greedy_generation_through_the_session(folders, plains, dtype):
     for name in ("sos_a", "sos_b"):
         m = plains[name]
         session = E.Session(folders[name], None, max_batch_size=3, dtype=dtype, max_tokens=2048)
-        prompts = [U.ids(50 + i, m.cfg["vocab"], n) for i, n in enumerate((5, 23, 1, 9))]
+        prompts = U.sequences(m, 50, (5, 23, 1, 9))
         got = session.generate_batch(prompts, steps=8, temperature=0.0)
         want = [P.generate(m, p, 8) for p in prompts]
         if dtype == "float32":
@@ -463,7 +497,7 @@ def test_trace_replay_of_a_model_folder(folders, plains, tmp_path, dtype):
     from test_replay_gpu import Replay
     m = plains["sos_b"]
     vocab = m.cfg["vocab"]
-    seqs = {f"q{i}": U.ids(400 + i, vocab, n) for i, n in enumerate((130, 1, 47))}
+    seqs = {f"q{i}": s for i, s in enumerate(U.sequences(m, 400, (130, 1, 47)))}
     refs = {k: P.forward(m, s) for k, s in seqs.items()}
     rp = Replay(folders["sos_b"], dtype, tmp_path, sum(len(s) for s in seqs.values()))
     for k, s in seqs.items():
