@@ -50,16 +50,29 @@ mingru_kernel(const TIN* __restrict__ proj, long long stride, int z_col, int x_c
   if (phase == 0) S = seq_start[s] > 0 ? state[(size_t)slot * width + c] : 0.f;
   if (phase == 2) S = mine[1];
   float A = 1.f;
-  for (int i = lo; i < hi; ++i) {
-    const TIN* row = proj + (size_t)(t0 + i) * stride;
-    float z, cand;
-    gate_and_candidate(to_float(row[z_col + c]) + bz, to_float(row[x_col + c]) + bx, z, cand);
-    S = fmaf(1.0f - z, S, z * cand);
-    if (phase == 1) {
-      A *= 1.0f - z;
-    } else {
-      const float g = to_float(row[g_col + c]);
-      out[(size_t)(t0 + i) * width + c] = from_float<TOUT>(S * (g * sigmoidf(g)));
+  constexpr int kAhead = 8;      // tokens whose columns are fetched before the chain of the state walks them
+  for (int i0 = lo; i0 < hi; i0 += kAhead) {
+    float za[kAhead], xa[kAhead], ga[kAhead];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      const bool there = i0 + u < hi;
+      const TIN* row = proj + (size_t)(t0 + (there ? i0 + u : lo)) * stride;
+      za[u] = to_float(row[z_col + c]);
+      xa[u] = to_float(row[x_col + c]);
+      ga[u] = phase == 1 ? 0.f : to_float(row[g_col + c]);
+    }
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      if (i0 + u >= hi) break;
+      float z, cand;
+      gate_and_candidate(za[u] + bz, xa[u] + bx, z, cand);
+      S = fmaf(1.0f - z, S, z * cand);
+      if (phase == 1) {
+        A *= 1.0f - z;
+      } else {
+        const float g = ga[u];
+        out[(size_t)(t0 + i0 + u) * width + c] = from_float<TOUT>(S * (g * sigmoidf(g)));
+      }
     }
   }
   if (phase == 1) {

@@ -943,7 +943,16 @@ class CudaOps:
                    bias.data_ptr(), gates.data_ptr(), T, heads, width, float(cap), _code(h.dtype))
         return gates
 
-    MLSTM_PIECE = 128       # tokens of a piece when a long sequence's recurrence is walked in pieces side by side
+    def _pieces(self, longest: int, blocks_per_piece: int) -> int:
+        """Into how many pieces a step's longest sequence is cut when a recurrence walks pieces side by side (twice:
+        once from nothing, once from each piece's start state): none below 256 tokens; else pieces of 128, 64 or 32
+        tokens, the longest that still give the launch four blocks for every SM."""
+        if longest < 256:
+            return 1
+        for piece in (128, 64, 32):
+            pieces = -(-longest // piece)
+            if pieces * blocks_per_piece >= 4 * self.sms or piece == 32:
+                return pieces
 
     def mlstm_scan(self, proj, q_col, k_col, v_col, gates, state, plan, heads, dim, vdim, floor, pieces=None):
         """The recurrence of parts/mlstm.py over the step's sequences: q, k (heads x dim) and v (heads x vdim) are
@@ -959,8 +968,9 @@ class CudaOps:
             raise KernelError("mlstm_scan: the columns of q, k and v do not fit the rows")
         out = torch.empty((plan.T, heads * vdim), dtype=torch.float32, device=proj.device)
         longest = max(int(plan.max_new), 1)
-        if pieces is None:      # (a second walk pays from four pieces on)
-            pieces = -(-longest // self.MLSTM_PIECE) if longest >= 4 * self.MLSTM_PIECE else 1
+        if pieces is None:
+            cols = -(-vdim // 32) * 32 if vdim <= 128 else 64         # (the kernel's columns a block)
+            pieces = self._pieces(longest, plan.n * heads * -(-vdim // cols))
         piece = -(-longest // pieces)
         scratch = None
         if pieces > 1:
@@ -974,8 +984,6 @@ class CudaOps:
             self.launches += 2
         return out
 
-    MINGRU_PIECE = 128      # tokens of a piece when a long sequence's recurrence is walked in pieces side by side
-
     def mingru(self, proj, z_col, x_col, g_col, bias_z, bias_x, state, plan, width, out_dtype, pieces=None):
         """The recurrence of parts/mingru.py over the step's sequences: the gate's, the candidate's and the output gate's
         columns of `proj`; state float32 [slots, width] (advanced); S_t * silu(g_t) as [T, width] of `out_dtype`."""
@@ -986,7 +994,7 @@ class CudaOps:
         out = torch.empty((plan.T, width), dtype=out_dtype, device=proj.device)
         longest = max(int(plan.max_new), 1)
         if pieces is None:
-            pieces = -(-longest // self.MINGRU_PIECE) if longest >= 4 * self.MINGRU_PIECE else 1
+            pieces = self._pieces(longest, plan.n * -(-width // 128))
         piece = -(-longest // pieces)
         scratch = None
         if pieces > 1:

@@ -381,8 +381,8 @@ def test_one_marked_key_is_seen_exactly_inside_the_window_and_pays_for_its_dista
                     assert (value > 5.0) if seen else (abs(value) < 1e-2), (marked, i, a, seen, value)
         near, far = marked + 1, marked + window - 1
         if far < T:
-            assert got[near, 0] > 95.0 and got[far, 0] < 50.0          # e^(7 - 0.05 * 89) against up to 90 others and the sink
-            assert got[near, hd] > 95.0 and got[far, hd] > 85.0        # e^7 against some 90 others
+            assert got[near, 0] > 90.0 and got[far, 0] < 50.0          # e^(7 - 0.05 * 89) against up to 90 others and the sink
+            assert got[near, hd] > 90.0 and got[far, hd] > 80.0        # e^7 against up to 90 others
 
 
 def test_a_sink_alone_in_the_denominator_halves_a_lone_keys_weight(ops):
