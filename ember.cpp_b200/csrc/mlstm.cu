@@ -12,9 +12,9 @@
 // gate the logarithm of the sigmoid.  `mlstm_scan` walks each sequence's tokens in order: a block = a run
 // of value columns j of one (sequence, head), a thread a column with S[:, j] in registers, and one more
 // warp that keeps n (a lane a few of its values) and makes the denominators; k, q and v of a few tokens
-// are staged in shared memory at a time, and one thread walks the maxima of those tokens.  Every column
-// is independent of the others, so a token's result depends on its sequence alone, never on the batch
-// or the step's cut.  A sequence that starts at position 0 starts from zeros whatever its slot's state
+// are staged in shared memory at a time, and that warp makes the maxima of those tokens with a scan, a lane
+// a token.  Every column is independent of the others, so a token's result depends on its sequence alone,
+// never on the batch or the step's cut beyond rounding.  A sequence that starts at position 0 starts from zeros whatever its slot's state
 // holds; sequences of slot -1 are padding: their rows are zero and no state is touched.
 //
 // A long sequence is cut into pieces that are walked side by side.  The recurrence is linear in (S, n) once
@@ -45,7 +45,22 @@ __global__ void mlstm_gates_kernel(const T* __restrict__ h, const T* __restrict_
   }
 }
 
-constexpr int kStage = 16;   // tokens staged in shared memory at a time
+constexpr int kStage = 32;   // tokens staged in shared memory at a time: a lane of the normaliser's warp each
+
+// 16 bytes of a row as float32 values.
+__device__ __forceinline__ void load_row_part(const float* src, float (&v)[4]) {
+  const float4 x = *reinterpret_cast<const float4*>(src);
+  v[0] = x.x, v[1] = x.y, v[2] = x.z, v[3] = x.w;
+}
+__device__ __forceinline__ void load_row_part(const __nv_bfloat16* src, float (&v)[8]) {
+  const uint4 x = *reinterpret_cast<const uint4*>(src);
+  const unsigned w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    v[2 * u] = __uint_as_float(w[u] << 16);
+    v[2 * u + 1] = __uint_as_float(w[u] & 0xffff0000u);
+  }
+}
 
 // grid (sequences, heads, column tiles); blockDim.x = cols + 32: `cols` column threads and the normaliser's warp.
 // DMAX >= dim, a multiple of 32: the column's registers.
@@ -99,32 +114,78 @@ __global__ void mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, i
       S[r] = (carried && d < dim) ? nrow[d] : 0.f;
     }
   }
-  float m = carried ? *mval : (phase == 1 ? -INFINITY : 0.f);   // walked by the normaliser's first lane
+  float m = carried ? *mval : (phase == 1 ? -INFINITY : 0.f);   // walked by the normaliser's warp (every lane holds it)
+  constexpr int kVec = 16 / (int)sizeof(T);
+  // rows of q and k in 16-byte parts where every part starts on 16 bytes
+  const bool vectors = dim % kVec == 0 && stride % kVec == 0 && q_col % kVec == 0 && k_col % kVec == 0 &&
+                       (reinterpret_cast<uintptr_t>(qkv) & 15) == 0;
   float F = 0.f;                                                 // (phase 1) the sum of the piece's log forget gates
 
   for (int c0 = 0; c0 < n; c0 += kStage) {
     const int cn = min(kStage, n - c0);
     __syncthreads();
-    for (int e = threadIdx.x; e < cn * DMAX; e += blockDim.x) {
-      const int i = e / DMAX, d = e % DMAX;
-      const T* src = qkv + (size_t)(t0 + c0 + i) * stride + (size_t)h * dim + d;
-      qs[e] = d < dim ? to_float(src[q_col]) * q_scale : 0.f;
-      ks[e] = d < dim ? to_float(src[k_col]) : 0.f;
+    if (vectors) {
+      for (int e = threadIdx.x; e < cn * (DMAX / kVec); e += blockDim.x) {
+        const int i = e / (DMAX / kVec), d = (e % (DMAX / kVec)) * kVec;
+        const T* src = qkv + (size_t)(t0 + c0 + i) * stride + (size_t)h * dim + d;
+        float qv[kVec], kv[kVec];
+        if (d < dim) {
+          load_row_part(src + q_col, qv);
+          load_row_part(src + k_col, kv);
+        } else {
+#pragma unroll
+          for (int u = 0; u < kVec; ++u) qv[u] = kv[u] = 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < kVec; u += 4) {
+          *reinterpret_cast<float4*>(qs + i * DMAX + d + u) =
+              make_float4(qv[u] * q_scale, qv[u + 1] * q_scale, qv[u + 2] * q_scale, qv[u + 3] * q_scale);
+          *reinterpret_cast<float4*>(ks + i * DMAX + d + u) = make_float4(kv[u], kv[u + 1], kv[u + 2], kv[u + 3]);
+        }
+      }
+    } else {
+      for (int e = threadIdx.x; e < cn * DMAX; e += blockDim.x) {
+        const int i = e / DMAX, d = e % DMAX;
+        const T* src = qkv + (size_t)(t0 + c0 + i) * stride + (size_t)h * dim + d;
+        qs[e] = d < dim ? to_float(src[q_col]) * q_scale : 0.f;
+        ks[e] = d < dim ? to_float(src[k_col]) : 0.f;
+      }
     }
     if (column)
       for (int i = 0; i < cn; ++i)
         vs[i * cols + threadIdx.x] = live ? to_float(qkv[(size_t)(t0 + c0 + i) * stride + v_col + (size_t)h * vdim + j]) : 0.f;
-    if ((int)threadIdx.x == cols) {
-      for (int i = 0; i < cn; ++i) {
-        const float* g = gates + (size_t)(t0 + c0 + i) * 2 * heads;
-        const float li = g[h], lf = g[heads + h];
-        const float m_new = fmaxf(lf + m, li);
-        keep[i] = expf(lf + m - m_new);
-        take[i] = expf(li - m_new);
-        den[i] = expf(-m_new);
-        m = m_new;
-        F += lf;
+    if (!column) {
+      // The maxima of the stage's tokens at once, a lane a token.  m -> max(a + m, b) is what a run of tokens does to
+      // the maximum in front of it (one token: a = f, b = i; a run behind another: a = a1 + a2, b = max(a2 + b1, b2)),
+      // so a scan over the lanes leaves every token's (a, b) from the stage's start, and m_t = max(a_t + m, b_t).
+      // The maximum is a stabiliser: the memory, the normaliser and exp(-m) all carry the factor exp(-m_t), and the
+      // result is the same for any m_t as long as each token's factors use the m of the token before it, as here.
+      float a = 0.f, b = -INFINITY, li = 0.f, lf = 0.f;
+      if (lane < cn) {
+        const float* g = gates + (size_t)(t0 + c0 + lane) * 2 * heads;
+        li = g[h];
+        lf = g[heads + h];
+        a = lf;
+        b = li;
       }
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const float a1 = __shfl_up_sync(0xffffffffu, a, off), b1 = __shfl_up_sync(0xffffffffu, b, off);
+        if (lane >= off) {
+          b = fmaxf(a + b1, b);
+          a += a1;
+        }
+      }
+      const float m_new = fmaxf(a + m, b);
+      float m_before = __shfl_up_sync(0xffffffffu, m_new, 1);
+      if (lane == 0) m_before = m;
+      if (lane < cn) {
+        keep[lane] = expf(lf + m_before - m_new);
+        take[lane] = expf(li - m_new);
+        den[lane] = expf(-m_new);
+      }
+      m = __shfl_sync(0xffffffffu, m_new, cn - 1);
+      F += __shfl_sync(0xffffffffu, a, cn - 1);
     }
     __syncthreads();
     if (column && phase == 1) {      // no results: the memory alone
