@@ -62,16 +62,21 @@ __device__ __forceinline__ void load_row_part(const __nv_bfloat16* src, float (&
   }
 }
 
-// grid (sequences, heads, column tiles); blockDim.x = cols + 32: `cols` column threads and the normaliser's warp.
-// DMAX >= dim, a multiple of 32: the column's registers.
+constexpr int kSplit = 4;    // lanes that share a column: each keeps a quarter of S[:, j]
+
+// grid (sequences x pieces, heads, column tiles); blockDim.x = kSplit * cols + 32: kSplit neighbouring lanes a column
+// (lane s of them keeps S[d, j] for d in the 16-byte parts s, s + kSplit, ... of a key row: DMAX / kSplit registers) and
+// the normaliser's warp.  DMAX >= dim, a multiple of 32.
 template <typename T, int DMAX>
-__global__ void mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, int q_col, int k_col, int v_col,
+__global__ void __launch_bounds__(kSplit * 64 + 32, DMAX <= 128 ? 3 : 1) mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, int q_col, int k_col, int v_col,
                                   const float* __restrict__ gates, float* __restrict__ S_state, float* __restrict__ n_state,
                                   float* __restrict__ m_state, float* __restrict__ out, const int* __restrict__ seq_slot,
                                   const int* __restrict__ seq_start, const int* __restrict__ cu_new, int heads, int dim,
                                   int vdim, float floor_, int piece, int pieces, int phase, float* __restrict__ scratch) {
   extern __shared__ float smem[];
-  const int cols = blockDim.x - 32;
+  constexpr int kMine = DMAX / kSplit;      // values of S a column lane keeps
+  const int workers = blockDim.x - 32;      // the column lanes
+  const int cols = workers / kSplit;
   float* ks = smem;                         // [kStage][DMAX]
   float* qs = ks + kStage * DMAX;           // [kStage][DMAX]
   float* vs = qs + kStage * DMAX;           // [kStage][cols]; the numerators afterwards
@@ -81,8 +86,9 @@ __global__ void mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, i
   // phase 0: the whole walk (one piece).  phase 1: a piece from nothing, its end left in scratch.  phase 2: a piece from
   // the start state that the carry left in scratch.
   const int s = blockIdx.x / pieces, pc = blockIdx.x % pieces, h = blockIdx.y;
-  const bool column = (int)threadIdx.x < cols;
-  const int j = blockIdx.z * cols + threadIdx.x;
+  const bool column = (int)threadIdx.x < workers;
+  const int c = threadIdx.x / kSplit, part = threadIdx.x % kSplit;
+  const int j = blockIdx.z * cols + c;
   const bool live = column && j < vdim;
   const int lane = threadIdx.x & 31;
   const int seq_n = cu_new[s + 1] - cu_new[s];
@@ -91,9 +97,11 @@ __global__ void mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, i
   const int t0 = cu_new[s] + lo, n = hi - lo;
   const int slot = seq_slot[s];
   const int inner = heads * vdim;
+  const int j0 = blockIdx.z * cols, jn = min(cols, vdim - j0);       // the block's columns
   if (slot < 0) {
-    if (live && phase != 1)
-      for (int i = 0; i < n; ++i) out[(size_t)(t0 + i) * inner + (size_t)h * vdim + j] = 0.f;
+    if (phase != 1)
+      for (int e = threadIdx.x; e < n * jn; e += blockDim.x)
+        out[(size_t)(t0 + e / jn) * inner + (size_t)h * vdim + j0 + e % jn] = 0.f;
     return;
   }
   const bool carried = phase == 2 || (phase == 0 && seq_start[s] > 0);
@@ -103,10 +111,14 @@ __global__ void mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, i
   float* col = (phase == 0 ? S_state + ((size_t)slot * heads + h) * dim * vdim : mine) + j;
   float* nrow = phase == 0 ? n_state + ((size_t)slot * heads + h) * dim : mine + (size_t)dim * vdim;
   float* mval = phase == 0 ? m_state + (size_t)slot * heads + h : mine + (size_t)dim * vdim + dim + (phase == 2 ? 2 : 0);
-  float S[DMAX];              // a column thread: S[:, j]; a lane of the normaliser's warp: n[lane + 32 r] in S[r]
+  // a column lane: S[d, j] in S[4 r + u] for d = 4 (kSplit r + part) + u; a lane of the normaliser's warp: n[lane + 32 r] in S[r]
+  float S[kMine];
   if (column) {
 #pragma unroll
-    for (int d = 0; d < DMAX; ++d) S[d] = (live && carried && d < dim) ? col[(size_t)d * vdim] : 0.f;
+    for (int r = 0; r < kMine; ++r) {
+      const int d = 4 * (kSplit * (r / 4) + part) + r % 4;
+      S[r] = (live && carried && d < dim) ? col[(size_t)d * vdim] : 0.f;
+    }
   } else {
 #pragma unroll
     for (int r = 0; r < DMAX / 32; ++r) {
@@ -123,13 +135,14 @@ __global__ void mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, i
 
   for (int c0 = 0; c0 < n; c0 += kStage) {
     const int cn = min(kStage, n - c0);
+    const int cn4 = (cn + 3) & ~3;      // tokens are walked four at a time: the rows behind the last one are zeros
     __syncthreads();
     if (vectors) {
-      for (int e = threadIdx.x; e < cn * (DMAX / kVec); e += blockDim.x) {
+      for (int e = threadIdx.x; e < cn4 * (DMAX / kVec); e += blockDim.x) {
         const int i = e / (DMAX / kVec), d = (e % (DMAX / kVec)) * kVec;
         const T* src = qkv + (size_t)(t0 + c0 + i) * stride + (size_t)h * dim + d;
         float qv[kVec], kv[kVec];
-        if (d < dim) {
+        if (d < dim && i < cn) {
           load_row_part(src + q_col, qv);
           load_row_part(src + k_col, kv);
         } else {
@@ -144,16 +157,17 @@ __global__ void mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, i
         }
       }
     } else {
-      for (int e = threadIdx.x; e < cn * DMAX; e += blockDim.x) {
+      for (int e = threadIdx.x; e < cn4 * DMAX; e += blockDim.x) {
         const int i = e / DMAX, d = e % DMAX;
         const T* src = qkv + (size_t)(t0 + c0 + i) * stride + (size_t)h * dim + d;
-        qs[e] = d < dim ? to_float(src[q_col]) * q_scale : 0.f;
-        ks[e] = d < dim ? to_float(src[k_col]) : 0.f;
+        qs[e] = d < dim && i < cn ? to_float(src[q_col]) * q_scale : 0.f;
+        ks[e] = d < dim && i < cn ? to_float(src[k_col]) : 0.f;
       }
     }
-    if (column)
-      for (int i = 0; i < cn; ++i)
-        vs[i * cols + threadIdx.x] = live ? to_float(qkv[(size_t)(t0 + c0 + i) * stride + v_col + (size_t)h * vdim + j]) : 0.f;
+    for (int e = threadIdx.x; e < cn4 * cols; e += blockDim.x) {
+      const int i = e / cols, cc = e % cols;
+      vs[e] = cc < jn && i < cn ? to_float(qkv[(size_t)(t0 + c0 + i) * stride + v_col + (size_t)h * vdim + j0 + cc]) : 0.f;
+    }
     if (!column) {
       // The maxima of the stage's tokens at once, a lane a token.  m -> max(a + m, b) is what a run of tokens does to
       // the maximum in front of it (one token: a = f, b = i; a run behind another: a = a1 + a2, b = max(a2 + b1, b2)),
@@ -179,67 +193,100 @@ __global__ void mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, i
       const float m_new = fmaxf(a + m, b);
       float m_before = __shfl_up_sync(0xffffffffu, m_new, 1);
       if (lane == 0) m_before = m;
-      if (lane < cn) {
-        keep[lane] = expf(lf + m_before - m_new);
-        take[lane] = expf(li - m_new);
-        den[lane] = expf(-m_new);
-      }
+      keep[lane] = lane < cn ? expf(lf + m_before - m_new) : 1.f;     // (behind the last token: nothing changes)
+      take[lane] = lane < cn ? expf(li - m_new) : 0.f;
+      den[lane] = expf(-m_new);
       m = __shfl_sync(0xffffffffu, m_new, cn - 1);
       F += __shfl_sync(0xffffffffu, a, cn - 1);
     }
     __syncthreads();
+    // Four tokens at a time: their rows are read and their sums made side by side, and one lane of the column's four
+    // writes each token's numerator afterwards, so that nothing is written between the reads of a group.
     if (column && phase == 1) {      // no results: the memory alone
-      for (int i = 0; i < cn; ++i) {
-        const float* k = ks + i * DMAX;
-        const float a = keep[i], b = take[i] * vs[i * cols + threadIdx.x];
+      for (int i0 = 0; i0 < cn; i0 += 4) {
+        float a[4], b[4];
 #pragma unroll
-        for (int d = 0; d < DMAX; d += 4) {
-          const float4 kv = *reinterpret_cast<const float4*>(k + d);
-          S[d] = fmaf(a, S[d], b * kv.x);
-          S[d + 1] = fmaf(a, S[d + 1], b * kv.y);
-          S[d + 2] = fmaf(a, S[d + 2], b * kv.z);
-          S[d + 3] = fmaf(a, S[d + 3], b * kv.w);
+        for (int u = 0; u < 4; ++u) {
+          a[u] = keep[i0 + u];
+          b[u] = take[i0 + u] * vs[(i0 + u) * cols + c];
+        }
+#pragma unroll
+        for (int r = 0; r < kMine; r += 4) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float4 kv = *reinterpret_cast<const float4*>(ks + (i0 + u) * DMAX + 4 * part + kSplit * r);
+            S[r] = fmaf(a[u], S[r], b[u] * kv.x);
+            S[r + 1] = fmaf(a[u], S[r + 1], b[u] * kv.y);
+            S[r + 2] = fmaf(a[u], S[r + 2], b[u] * kv.z);
+            S[r + 3] = fmaf(a[u], S[r + 3], b[u] * kv.w);
+          }
         }
       }
     } else if (column) {
-      for (int i = 0; i < cn; ++i) {
-        const float* k = ks + i * DMAX;
-        const float* q = qs + i * DMAX;
-        const float a = keep[i], b = take[i] * vs[i * cols + threadIdx.x];
-        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      for (int i0 = 0; i0 < cn; i0 += 4) {
+        float a[4], b[4], o[4], p[4];
 #pragma unroll
-        for (int d = 0; d < DMAX; d += 4) {
-          const float4 kv = *reinterpret_cast<const float4*>(k + d);
-          const float4 qv = *reinterpret_cast<const float4*>(q + d);
-          S[d] = fmaf(a, S[d], b * kv.x);
-          S[d + 1] = fmaf(a, S[d + 1], b * kv.y);
-          S[d + 2] = fmaf(a, S[d + 2], b * kv.z);
-          S[d + 3] = fmaf(a, S[d + 3], b * kv.w);
-          o0 = fmaf(S[d], qv.x, o0);
-          o1 = fmaf(S[d + 1], qv.y, o1);
-          o2 = fmaf(S[d + 2], qv.z, o2);
-          o3 = fmaf(S[d + 3], qv.w, o3);
+        for (int u = 0; u < 4; ++u) {
+          a[u] = keep[i0 + u];
+          b[u] = take[i0 + u] * vs[(i0 + u) * cols + c];
+          o[u] = p[u] = 0.f;
         }
-        vs[i * cols + threadIdx.x] = (o0 + o1) + (o2 + o3);     // the numerator, in the place of the value it came from
+#pragma unroll
+        for (int r = 0; r < kMine; r += 4) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float4 kv = *reinterpret_cast<const float4*>(ks + (i0 + u) * DMAX + 4 * part + kSplit * r);
+            const float4 qv = *reinterpret_cast<const float4*>(qs + (i0 + u) * DMAX + 4 * part + kSplit * r);
+            S[r] = fmaf(a[u], S[r], b[u] * kv.x);
+            S[r + 1] = fmaf(a[u], S[r + 1], b[u] * kv.y);
+            S[r + 2] = fmaf(a[u], S[r + 2], b[u] * kv.z);
+            S[r + 3] = fmaf(a[u], S[r + 3], b[u] * kv.w);
+            o[u] = fmaf(S[r], qv.x, o[u]);
+            p[u] = fmaf(S[r + 1], qv.y, p[u]);
+            o[u] = fmaf(S[r + 2], qv.z, o[u]);
+            p[u] = fmaf(S[r + 3], qv.w, p[u]);
+          }
+        }
+        // the column's lanes are neighbours in one warp; every one of them has read the group's values before the exchange
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          o[u] += p[u];
+          o[u] += __shfl_xor_sync(0xffffffffu, o[u], 1);
+          o[u] += __shfl_xor_sync(0xffffffffu, o[u], 2);
+        }
+        const float own = part == 0 ? o[0] : part == 1 ? o[1] : part == 2 ? o[2] : o[3];
+        if (i0 + part < cn) vs[(i0 + part) * cols + c] = own;     // the numerator, in the place of the value it came from
       }
     } else {
-      for (int i = 0; i < cn; ++i) {
-        const float a = keep[i], b = take[i];
-        float dot = 0.f;
+      for (int i0 = 0; i0 < cn; i0 += 4) {
+        float a[4], b[4], dot[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          a[u] = keep[i0 + u];
+          b[u] = take[i0 + u];
+          dot[u] = 0.f;
+        }
 #pragma unroll
         for (int r = 0; r < DMAX / 32; ++r) {
           const int d = lane + 32 * r;
-          S[r] = fmaf(a, S[r], b * ks[i * DMAX + d]);
-          dot = fmaf(S[r], qs[i * DMAX + d], dot);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            S[r] = fmaf(a[u], S[r], b[u] * ks[(i0 + u) * DMAX + d]);
+            dot[u] = fmaf(S[r], qs[(i0 + u) * DMAX + d], dot[u]);
+          }
         }
-        dot = warp_sum(dot);
-        if (lane == 0) den[i] = fmaxf(fabsf(dot), den[i]) + floor_;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) dot[u] = warp_sum(dot[u]);
+        const float own = lane == 0 ? dot[0] : lane == 1 ? dot[1] : lane == 2 ? dot[2] : dot[3];
+        if (lane < 4 && i0 + lane < cn) den[i0 + lane] = fmaxf(fabsf(own), den[i0 + lane]) + floor_;
       }
     }
     __syncthreads();
-    if (live && phase != 1)
-      for (int i = 0; i < cn; ++i)
-        out[(size_t)(t0 + c0 + i) * inner + (size_t)h * vdim + j] = vs[i * cols + threadIdx.x] / den[i];
+    if (phase != 1)
+      for (int e = threadIdx.x; e < cn * jn; e += blockDim.x) {
+        const int i = e / jn, cc = e % jn;
+        out[(size_t)(t0 + c0 + i) * inner + (size_t)h * vdim + j0 + cc] = vs[i * cols + cc] / den[i];
+      }
   }
   // the end: into the piece's place (phase 1), or into the slot's rows by the walk that reaches the sequence's end
   if (phase == 2) {
@@ -250,8 +297,10 @@ __global__ void mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, i
   }
   if (live) {
 #pragma unroll
-    for (int d = 0; d < DMAX; ++d)
-      if (d < dim) col[(size_t)d * vdim] = S[d];
+    for (int r = 0; r < kMine; ++r) {
+      const int d = 4 * (kSplit * (r / 4) + part) + r % 4;
+      if (d < dim) col[(size_t)d * vdim] = S[r];
+    }
   }
   if (!column && blockIdx.z == 0) {
 #pragma unroll
@@ -300,8 +349,9 @@ template <typename T, int DMAX>
 cudaError_t launch_scan(const void* qkv, long long stride, int q_col, int k_col, int v_col, const float* gates, float* S, float* n,
                         float* m, float* out, const int* seq_slot, const int* seq_start, const int* cu_new, int n_seqs, int heads,
                         int dim, int vdim, float floor_, int piece, int pieces, float* scratch, cudaStream_t stream) {
-  // columns a block: all of a head's where they are few, so that the normaliser is walked once
-  const int cols = vdim <= 128 ? (vdim + 31) / 32 * 32 : 64;
+  // columns a block (a multiple of 8: whole warps of column lanes): all of a head's where they are few, so that the
+  // normaliser is walked once
+  const int cols = vdim <= 64 ? (vdim + 7) / 8 * 8 : 64;
   const int tiles = (vdim + cols - 1) / cols;
   const size_t smem = (size_t)(2 * kStage * DMAX + kStage * cols + 3 * kStage) * sizeof(float);
   auto kernel = mlstm_scan_kernel<T, DMAX>;
@@ -311,7 +361,7 @@ cudaError_t launch_scan(const void* qkv, long long stride, int q_col, int k_col,
   }
   cudaError_t e = cudaSuccess;
   for (int phase = pieces > 1 ? 1 : 0; phase <= (pieces > 1 ? 2 : 0) && e == cudaSuccess; ++phase) {
-    e = launch_plain(kernel, dim3(n_seqs * pieces, heads, tiles), dim3(cols + 32), smem, stream, (const T*)qkv, stride, q_col, k_col,
+    e = launch_plain(kernel, dim3(n_seqs * pieces, heads, tiles), dim3(kSplit * cols + 32), smem, stream, (const T*)qkv, stride, q_col, k_col,
                      v_col, gates, S, n, m, out, seq_slot, seq_start, cu_new, heads, dim, vdim, floor_, piece, pieces, phase, scratch);
     if (phase == 1 && e == cudaSuccess) {
       const int values = dim * vdim + dim;

@@ -943,16 +943,26 @@ class CudaOps:
                    bias.data_ptr(), gates.data_ptr(), T, heads, width, float(cap), _code(h.dtype))
         return gates
 
-    def _pieces(self, longest: int, blocks_per_piece: int) -> int:
+    def _pieces(self, longest: int, blocks_per_piece: int, resident: int | None = None) -> int:
         """Into how many pieces a step's longest sequence is cut when a recurrence walks pieces side by side (twice:
-        once from nothing, once from each piece's start state): none below 256 tokens; else pieces of 128, 64 or 32
-        tokens, the longest that still give the launch four blocks for every SM."""
+        once from nothing, once from each piece's start state): none below 256 tokens.  Without `resident`: pieces of
+        128, 64 or 32 tokens, the longest that still give the launch four blocks for every SM.  With `resident` (the
+        blocks of the kernel that the chip holds at once): the count that makes waves of blocks x a piece's tokens x
+        two walks smallest, a piece counted 16 tokens longer than it is for what its start and end cost; a launch
+        that ends a little into a second wave takes twice as long as one that just fits the first."""
         if longest < 256:
             return 1
-        for piece in (128, 64, 32):
-            pieces = -(-longest // piece)
-            if pieces * blocks_per_piece >= 4 * self.sms or piece == 32:
-                return pieces
+        if resident is None:
+            for piece in (128, 64, 32):
+                pieces = -(-longest // piece)
+                if pieces * blocks_per_piece >= 4 * self.sms or piece == 32:
+                    return pieces
+        best, best_cost = 1, -(-blocks_per_piece // resident) * (longest + 16)
+        for pieces in range(3, longest // 32 + 1):
+            cost = -(-pieces * blocks_per_piece // resident) * (-(-longest // pieces) + 16) * 2
+            if cost < best_cost:
+                best, best_cost = pieces, cost
+        return best
 
     def mlstm_scan(self, proj, q_col, k_col, v_col, gates, state, plan, heads, dim, vdim, floor, pieces=None):
         """The recurrence of parts/mlstm.py over the step's sequences: q, k (heads x dim) and v (heads x vdim) are
@@ -969,8 +979,9 @@ class CudaOps:
         out = torch.empty((plan.T, heads * vdim), dtype=torch.float32, device=proj.device)
         longest = max(int(plan.max_new), 1)
         if pieces is None:
-            cols = -(-vdim // 32) * 32 if vdim <= 128 else 64         # (the kernel's columns a block)
-            pieces = self._pieces(longest, plan.n * heads * -(-vdim // cols))
+            cols = -(-vdim // 8) * 8 if vdim <= 64 else 64            # (the kernel's columns a block)
+            # (blocks of nine warps: three on an SM up to a key size of 128, one above)
+            pieces = self._pieces(longest, plan.n * heads * -(-vdim // cols), resident=self.sms * (3 if dim <= 128 else 1))
         piece = -(-longest // pieces)
         scratch = None
         if pieces > 1:
