@@ -29,24 +29,6 @@ namespace {
 
 __device__ __forceinline__ float log_sigmoid(float v) { return fminf(v, 0.f) - log1pf(expf(-fabsf(v))); }
 
-// grid (T), 128 threads: a warp takes one gate row (2 * heads of them: input gates, then forget gates) at a time.
-template <typename T>
-__global__ void mlstm_gates_kernel(const T* __restrict__ h, const T* __restrict__ w, const float* __restrict__ bias,
-                                   float* __restrict__ gates, int heads, int width, float cap) {
-  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  const T* row = h + (size_t)t * width;
-  for (int r = warp; r < 2 * heads; r += warps) {
-    const T* wr = w + (size_t)r * width;
-    float acc = 0.f;
-    for (int d = lane; d < width; d += 32) acc = fmaf(to_float(row[d]), to_float(wr[d]), acc);
-    acc = warp_sum(acc) + bias[r];
-    const float capped = cap > 0.f ? cap * tanhf(acc / cap) : acc;
-    if (lane == 0) gates[(size_t)t * 2 * heads + r] = r < heads ? capped : log_sigmoid(capped);
-  }
-}
-
-constexpr int kStage = 32;   // tokens staged in shared memory at a time: a lane of the normaliser's warp each
-
 // 16 bytes of a row as float32 values.
 __device__ __forceinline__ void load_row_part(const float* src, float (&v)[4]) {
   const float4 x = *reinterpret_cast<const float4*>(src);
@@ -61,6 +43,41 @@ __device__ __forceinline__ void load_row_part(const __nv_bfloat16* src, float (&
     v[2 * u + 1] = __uint_as_float(w[u] & 0xffff0000u);
   }
 }
+
+// grid (T, row groups), 128 threads: a warp a gate row (2 * heads of them: input gates, then forget gates).  A row is
+// summed by one warp in an order that its length alone fixes: 16-byte parts where every row starts on 16 bytes.
+template <typename T>
+__global__ void mlstm_gates_kernel(const T* __restrict__ h, const T* __restrict__ w, const float* __restrict__ bias,
+                                   float* __restrict__ gates, int heads, int width, float cap) {
+  constexpr int kVec = 16 / (int)sizeof(T);
+  const int t = blockIdx.x, lane = threadIdx.x & 31;
+  const int r = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= 2 * heads) return;
+  const T* row = h + (size_t)t * width;
+  const T* wr = w + (size_t)r * width;
+  float acc = 0.f;
+  if (width % kVec == 0 && ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(w)) & 15) == 0) {
+    float acc2 = 0.f;
+    for (int d = lane * kVec; d < width; d += 32 * kVec) {
+      float a[kVec], b[kVec];
+      load_row_part(row + d, a);
+      load_row_part(wr + d, b);
+#pragma unroll
+      for (int u = 0; u < kVec; u += 2) {
+        acc = fmaf(a[u], b[u], acc);
+        acc2 = fmaf(a[u + 1], b[u + 1], acc2);
+      }
+    }
+    acc += acc2;
+  } else {
+    for (int d = lane; d < width; d += 32) acc = fmaf(to_float(row[d]), to_float(wr[d]), acc);
+  }
+  acc = warp_sum(acc) + bias[r];
+  const float capped = cap > 0.f ? cap * tanhf(acc / cap) : acc;
+  if (lane == 0) gates[(size_t)t * 2 * heads + r] = r < heads ? capped : log_sigmoid(capped);
+}
+
+constexpr int kStage = 32;   // tokens staged in shared memory at a time: a lane of the normaliser's warp each
 
 constexpr int kSplit = 4;    // lanes that share a column: each keeps a quarter of S[:, j]
 
@@ -396,11 +413,12 @@ EMBER_API int ember_mlstm_gates(const void* h, const void* w, const float* bias,
                                 float cap, int dtype, cudaStream_t stream) {
   EMBER_CHECK(T > 0 && heads > 0 && width > 0 && cap >= 0.f, "mlstm_gates: bad sizes");
   cudaError_t e;
+  const dim3 grid(T, (2 * heads + 3) / 4);      // four warps a block, a row each
   if (dtype == EMBER_F32)
-    e = launch_plain(mlstm_gates_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)h, (const float*)w, bias, gates, heads,
+    e = launch_plain(mlstm_gates_kernel<float>, grid, dim3(128), 0, stream, (const float*)h, (const float*)w, bias, gates, heads,
                      width, cap);
   else if (dtype == EMBER_BF16)
-    e = launch_plain(mlstm_gates_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)h,
+    e = launch_plain(mlstm_gates_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)h,
                      (const __nv_bfloat16*)w, bias, gates, heads, width, cap);
   else
     return ember_fail("mlstm_gates: element type %d", dtype);

@@ -200,11 +200,12 @@ def test_the_matrix_memory_keeps_a_token_from_far_back(ops):
     close(got, want, 3e-5)
 
 
-@pytest.mark.parametrize("pieces", [1, 2, 5])
-@pytest.mark.parametrize("heads, dim, vdim", [(2, 16, 24), (1, 40, 136)])
+@pytest.mark.parametrize("pieces", [1, 2, 5, None])
+@pytest.mark.parametrize("heads, dim, vdim", [(2, 16, 24), (1, 40, 136), (1, 160, 72)])
 def test_mlstm_in_pieces_side_by_side_equals_one_walk(ops, pieces, heads, dim, vdim):
     """Two sequences of unequal length, one of them on top of a carried state (its running maximum not zero); the shorter
-    one ends before the last pieces begin."""
+    one ends before the last pieces begin.  Key sizes of every register layout, a last tile of a few value columns, and
+    the count of pieces that the library picks itself (None)."""
     lengths = (300, 70)
     qk, inner = heads * dim, heads * vdim
     rows = rnd(1, sum(lengths), 2 * qk + inner, scale=0.7)
