@@ -337,6 +337,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             } else if (p.act == EMBER_ACT_GELU_ERF) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+            } else if (p.act == EMBER_ACT_RELU2) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] * v[j] : 0.f;
             }
             const size_t at = (size_t)(m0 + lane) * p.N + n;
             if (p.out_f32) {
@@ -369,6 +372,7 @@ __global__ void __launch_bounds__(kThreads, 1)
               float v = turn[r * 33 + lane] + b;
               if (p.act == EMBER_ACT_GELU_TANH) v = gelu_tanh_fast(v);
               else if (p.act == EMBER_ACT_GELU_ERF) v = gelu_erf(v);
+              else if (p.act == EMBER_ACT_RELU2) v = v > 0.f ? v * v : 0.f;
               v += res[r];
               const size_t at = (size_t)(m0 + r) * p.N + n;
               if (p.out_f32)
@@ -516,7 +520,7 @@ EMBER_API int ember_linear_tc(const void* A, const void* W, const float* bias, c
   EMBER_CHECK(M > 0 && N > 0 && K > 0, "linear_tc: M = %d, N = %d, K = %d", M, N, K);
   EMBER_CHECK(K % 8 == 0, "linear_tc: K = %d is not a multiple of 8 (rows of 16 bytes)", K);
   EMBER_CHECK(((uintptr_t)A | (uintptr_t)W) % 16 == 0, "linear_tc: operands are not 16-byte aligned");
-  EMBER_CHECK(act >= EMBER_ACT_NONE && act <= EMBER_ACT_GELU_ERF, "linear_tc: activation %d", act);
+  EMBER_CHECK(act >= EMBER_ACT_NONE && act <= EMBER_ACT_RELU2, "linear_tc: activation %d", act);
   EMBER_CHECK(out_dtype == EMBER_F32 || out_dtype == EMBER_BF16, "linear_tc: output type %d", out_dtype);
   EMBER_CHECK(!residual || out_dtype == EMBER_F32, "linear_tc: a residual sum needs a float32 output");
   EMBER_CHECK((uintptr_t)out % 16 == 0 && (!residual || (uintptr_t)residual % 16 == 0) && (!bias || (uintptr_t)bias % 16 == 0),
