@@ -30,9 +30,8 @@ def build_spec(cfg: SosutarConfig) -> ModelSpec:
     gain = lambda name: PartSpec("layer_scale", name, {"width": d, "weight": "", "eps": eps})  # noqa: E731
     layers, index_of, schedule = [], {}, []
     for i, layer in enumerate(cfg.layers):
-        src = layer.get("weights_of")
-        if src is not None:
-            schedule.append(Application(index_of[src]) if src in index_of else None)
+        if layer.get("weights_of") is not None:
+            schedule.append(None)       # (filled in below: the owner may come later in the list)
             continue
         p = f"l{i}."
         m = layer["mixer"]
@@ -59,10 +58,10 @@ def build_spec(cfg: SosutarConfig) -> ModelSpec:
         index_of[i] = len(layers)
         layers.append(LayerSpec("sandwich", norm(p + "norm1"), mixer, norm(p + "norm2") if ffn is not None else None, ffn, more))
         schedule.append(Application(index_of[i]))
-    # a layer may run with the tensors of a layer that comes after it in the list
-    for i, layer in enumerate(cfg.layers):
+    # a layer may run with the tensors of a layer that comes after it in the list, or of one that names a third
+    for i in range(len(cfg.layers)):
         if schedule[i] is None:
-            schedule[i] = Application(index_of[layer["weights_of"]])
+            schedule[i] = Application(index_of[cfg.owner_of(i)])
     return ModelSpec(width=d, vocab_size=cfg.vocab, token_table="embed",
                      position=PartSpec("learned_absolute", "", {"width": d, "n_positions": cfg.max_positions, "table": "pos"}),
                      layers=tuple(layers), schedule=tuple(schedule), final_norm=norm("final.norm"), head="head",

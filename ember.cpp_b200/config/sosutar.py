@@ -90,11 +90,22 @@ class SosutarConfig(ModelConfig):
             if src is not None:
                 if isinstance(src, bool) or not isinstance(src, int) or not 0 <= src < len(self.layers) or src == i:
                     raise ConfigError(f"SosutarConfig: {at}weights_of = {src!r} must name another layer")
-                other = self.layers[src]
-                if not isinstance(other, dict) or other.get("weights_of") is not None:
-                    raise ConfigError(f"SosutarConfig: {at}weights_of = {src} names a layer that has no tensors of its own")
-                if other.get("type") != layer["type"]:
+                owner = self.owner_of(i)
+                if owner is None:
+                    raise ConfigError(f"SosutarConfig: {at}weights_of = {src} leads to no layer with tensors of its own")
+                if self.layers[owner].get("type") != layer["type"]:
                     raise ConfigError(f"SosutarConfig: {at}weights_of = {src} names a layer of another type")
+
+    def owner_of(self, i: int):
+        """The layer whose tensors layer i runs with: itself, or where its `weights_of` leads (a layer named there may
+        name another in turn); None if that ends nowhere."""
+        seen = set()
+        while isinstance(self.layers[i], dict) and self.layers[i].get("weights_of") is not None:
+            seen.add(i)
+            i = self.layers[i]["weights_of"]
+            if isinstance(i, bool) or not isinstance(i, int) or not 0 <= i < len(self.layers) or i in seen:
+                return None
+        return i
 
     def check_dtype(self, dtype: str) -> None:
         """Nothing is refused: every part of this design has a kernel for every size in both compute types (rows

@@ -79,16 +79,16 @@ __global__ void mlstm_gates_kernel(const T* __restrict__ h, const T* __restrict_
 
 constexpr int kStage = 32;   // tokens staged in shared memory at a time: a lane of the normaliser's warp each
 
-#ifndef EMBER_MLSTM_BLOCKS
-#define EMBER_MLSTM_BLOCKS 3
-#endif
 constexpr int kSplit = 4;    // lanes that share a column: each keeps a quarter of S[:, j]
 
 // grid (sequences x pieces, heads, column tiles); blockDim.x = kSplit * cols + 32: kSplit neighbouring lanes a column
 // (lane s of them keeps S[d, j] for d in the 16-byte parts s, s + kSplit, ... of a key row: DMAX / kSplit registers) and
-// the normaliser's warp.  DMAX >= dim, a multiple of 32.
+// the normaliser's warp.  DMAX >= dim, a multiple of 32.  Two blocks an SM up to a key size of 128 (96 registers a thread:
+// with three blocks and 72 the loads of k and q stand closer in front of their use, 400 against 373 microseconds for
+// 2,048 tokens of 8 heads of 128 x 256), one above.
 template <typename T, int DMAX>
-__global__ void __launch_bounds__(kSplit * 64 + 32, DMAX <= 128 ? EMBER_MLSTM_BLOCKS : 1) mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, int q_col, int k_col, int v_col,
+__global__ void __launch_bounds__(kSplit * 64 + 32, DMAX <= 128 ? 2 : 1)
+mlstm_scan_kernel(const T* __restrict__ qkv, long long stride, int q_col, int k_col, int v_col,
                                   const float* __restrict__ gates, float* __restrict__ S_state, float* __restrict__ n_state,
                                   float* __restrict__ m_state, float* __restrict__ out, const int* __restrict__ seq_slot,
                                   const int* __restrict__ seq_start, const int* __restrict__ cu_new, int heads, int dim,

@@ -985,8 +985,8 @@ class CudaOps:
         longest = max(int(plan.max_new), 1)
         if pieces is None:
             cols = -(-vdim // 8) * 8 if vdim <= 64 else 64            # (the kernel's columns a block)
-            # (blocks of nine warps: three on an SM up to a key size of 128, one above)
-            pieces = self._pieces(longest, plan.n * heads * -(-vdim // cols), resident=self.sms * (3 if dim <= 128 else 1))
+            # (blocks of nine warps: two on an SM up to a key size of 128, one above)
+            pieces = self._pieces(longest, plan.n * heads * -(-vdim // cols), resident=self.sms * (2 if dim <= 128 else 1))
         piece = -(-longest // pieces)
         scratch = None
         if pieces > 1:

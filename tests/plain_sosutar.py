@@ -190,8 +190,10 @@ def mixer(m: PlainSosutar, entry: dict, prefix: str, h):
 
 
 def layer(m: PlainSosutar, i: int, x):
-    entry = m.cfg["layers"][i]
-    p = f"l{entry.get('weights_of', i)}."
+    entry, owner = m.cfg["layers"][i], i
+    while m.cfg["layers"][owner].get("weights_of") is not None:       # (a layer named there may name another in turn)
+        owner = m.cfg["layers"][owner]["weights_of"]
+    p = f"l{owner}."
     eps = m.cfg["norm"]["eps"]
     x = x + m.w[p + "ls1"] * mixer(m, entry, p, rms_norm(x, m.w[p + "norm1"], eps))
     if entry.get("mlp") is not None:

@@ -1,5 +1,7 @@
 """Sosutar on the host side: configuration, spec, random weights, state rows, and the step function,
 batching and generation loop over the CPU double of the kernels, against the plain implementation."""
+import json
+
 import numpy as np
 import pytest
 import torch
@@ -77,6 +79,15 @@ def test_a_layer_that_runs_with_another_layers_tensors_is_an_entry_of_the_run_or
                 assert cache.kind == "window" and cache.window == layer["mixer"]["left"]["mask"]["size"]
                 assert set(state) == {"right."} and state["right."].shape == (layer["mixer"]["right"]["width"],)
     assert spec.scale_positions is False and spec.logit_scale == 2.0 and spec.embedding_scale == 0.5
+    # a layer may name a layer that names a third: all three run with the third's tensors
+    d = U.config("sos_a")
+    d["layers"].append(dict(d["layers"][2], weights_of=2))
+    cfg = config_from_dict(d)
+    spec = E.config.get_architecture("Sosutar").build_spec(cfg)
+    assert [a.layer for a in spec.schedule] == [0, 1, 0, 2, 1, 0] and cfg.owner_of(5) == 0
+    d["layers"][0] = dict(d["layers"][0], weights_of=5)         # ... but not in a ring
+    with pytest.raises(ConfigError, match="weights_of"):
+        config_from_dict(d)
 
 
 def test_random_weights_follow_the_parts_lists(folders):
@@ -137,3 +148,17 @@ def test_greedy_generation_through_the_session(folders, plains):
         session = E.Session(folders[name], None, max_batch_size=3, dtype="float32", max_tokens=1024, ops=CpuOps(), device="cpu")
         prompts = [U.ids(50 + i, m.cfg["vocab"], n) for i, n in enumerate((5, 23, 1, 9))]
         assert session.generate_batch(prompts, steps=6, temperature=0.0) == [P.generate(m, p, 6) for p in prompts]
+
+
+def test_the_command_line_writes_a_random_model_of_this_design(tmp_path):
+    from ember_cpp_b200 import cli
+    cfg_file = tmp_path / "cfg.json"
+    cfg_file.write_text(json.dumps(U.config("sos_b")))
+    out = tmp_path / "model"
+    assert cli.main([str(out), "-", "1", "random-weights", "--config", str(cfg_file), "--seed", "5"]) == 0
+    cfg = E.load_config(str(out))
+    assert isinstance(cfg, SosutarConfig) and cfg.width == 96
+    eng = cpu_engine(str(out), max_tokens=128)
+    slot = eng.open()
+    logits = eng.step([(slot, U.ids(1, 200, 9), [8])])
+    assert tuple(logits.shape) == (1, 200) and bool(torch.isfinite(logits).all())

@@ -520,3 +520,22 @@ def test_trace_replay_of_a_model_folder(folders, plains, tmp_path, dtype):
     rp.close()
     for k in seqs:
         assert U.row_error(np.concatenate(rows[k]), refs[k]) < U.TOL[dtype]
+
+
+def test_the_command_line_generates_greedily(folders, plains):
+    """bin/ember picks the model by config.json: a prompt's greedy tokens in 32-bit, and a batch of two prompts."""
+    import os
+    import subprocess
+    import sys
+    m = plains["sos_a"]
+    prompt = U.sequences(m, 900, (7,))[0]
+    cli = [sys.executable, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bin", "ember")]
+    r = subprocess.run(cli + [folders["sos_a"], "-", "1", "prompt", " ".join(map(str, prompt)), "-mt", "5", "-t", "0", "--dtype", "float32"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    assert [int(t) for t in r.stdout.split()] == P.generate(m, prompt, 5)
+    other = U.sequences(m, 901, (3,))[0]
+    r = subprocess.run(cli + [folders["sos_a"], "-", "1", "batch", "--batch-prompts", " ".join(map(str, prompt)), " ".join(map(str, other)),
+                              "-mt", "3", "--temperature", "0", "--dtype", "float32", "-mbs", "2"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    assert "Output: " + " ".join(map(str, P.generate(m, other, 3))) in r.stdout
