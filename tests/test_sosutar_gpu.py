@@ -275,6 +275,26 @@ def test_mingru_in_pieces_side_by_side_equals_one_walk(ops, pieces):
         at += n
 
 
+@pytest.mark.parametrize("pieces", [1, None])
+def test_mingru_keeps_a_token_from_far_back(ops, pieces):
+    """Gates shut but for one early token: every later state is that token's candidate, 600 tokens on and through the
+    pieces of a long step; a second sequence opens its gate late and forgets what it held."""
+    width, n = 40, 640
+    rows = torch.zeros(2 * n, 3 * width)
+    rows[:, :width] = -18.0                                    # gates shut: z = 1.5e-8
+    rows[:, width:2 * width] = rnd(1, 2 * n, width)            # candidates that are never taken
+    rows[:, 2 * width:] = 1.0
+    rows[5, :width], rows[5, width:2 * width] = 18.0, torch.linspace(-3, 3, width)
+    rows[n + 600, :width], rows[n + 600, width:2 * width] = 18.0, 2.0
+    zeros = torch.zeros(width).cuda()
+    state = torch.full((2, width), float("nan")).cuda()
+    got = f64(ops.mingru(rows.cuda(), 0, width, 2 * width, zeros, zeros, state, plan_of([(0, 0, n), (1, 0, n)]), width,
+                         torch.float32, pieces=pieces))
+    held = P.mingru_candidate(np.linspace(-3, 3, width)) * float(P.silu(np.array(1.0)))
+    assert np.abs(got[5:n] - held).max() < 1e-4 and np.abs(got[:5]).max() < 1e-6
+    assert np.abs(got[n + 600:] - 2.5 * float(P.silu(np.array(1.0)))).max() < 1e-4 and np.abs(got[n:n + 600]).max() < 1e-4
+
+
 # ------------------------------------------------------------------------------ attention with a distance penalty and a sink
 def attention_steps(ops, dtype, heads, kv, hd, vd, window, steps, qkv_of, scale, slopes, sinks):
     """Feeds sequences step by step through the paged cache (pages taken in a scrambled order, NaN in every page
