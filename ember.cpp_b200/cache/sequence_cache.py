@@ -52,6 +52,8 @@ class CacheGroup:
 
     def first_needed_block(self, next_position: int) -> int:
         """The first block that a query at `next_position` can still read."""
+        if self.need.kind == "chunk":      # the run of `window` positions that holds the query, counted from position 0
+            return (next_position // self.need.window * self.need.window) // PAGE
         if self.need.kind != "window":
             return 0
         return max(0, next_position - self.need.window + 1) // PAGE
@@ -271,7 +273,7 @@ class SequenceCache:
         for slot, n in step:
             self.lengths[slot] += n
             for g in self.groups:
-                if g.need.kind == "window":
+                if g.need.kind in ("window", "chunk"):
                     g.trim(slot, self.lengths[slot])
 
     def truncate(self, slot: int, length: int) -> None:

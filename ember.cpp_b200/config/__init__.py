@@ -5,6 +5,7 @@ from .gpt2 import GELU_FORMS, GPT2Config
 from .muzozen import MuzozenConfig
 from .nipolorn import NipolornConfig
 from .sosutar import SosutarConfig
+from .vipolix import VipolixConfig
 
-__all__ = ["Architecture", "ConfigError", "GELU_FORMS", "GPT2Config", "ModelConfig", "MuzozenConfig", "NipolornConfig", "SosutarConfig", "architectures",
+__all__ = ["Architecture", "ConfigError", "GELU_FORMS", "GPT2Config", "ModelConfig", "MuzozenConfig", "NipolornConfig", "SosutarConfig", "VipolixConfig", "architectures",
            "config_from_dict", "get_architecture", "load_config", "register_architecture"]

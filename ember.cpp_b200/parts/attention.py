@@ -25,10 +25,24 @@ head whose exponential is added to the softmax's denominator (it has no key and 
 matrix W_g, the heads laid end to end are multiplied by sigmoid(W_g h) before the output projection.  With a norm
 on q or k or v, or a gate, the projection q | k | v (| g) is left in float32 (the norms read it unrounded) and
 the normed rows are rounded to the compute type once.
+
+And, again each a parameter: `qkv_bias` = suffix: q, k and v (stored as three matrices) have biases of that
+suffix, added in the projection, and the output projection has none; `conv` = (taps, suffix): a short causal
+convolution over time on every channel of q, k and v (a filter [channels, taps] a tensor, the last tap on the
+current token, zeros before the sequence's start, no bias, no activation) directly after the projection; the
+last taps - 1 projected rows of a sequence are its state ("conv"); `rotary` = (dims, base, interleaved): the
+mixer rotates the first `dims` dimensions of every q and k head itself, neighbours (2i, 2i + 1) paired where
+`interleaved`; `head_scale`: the name of one learned factor a query head on its scores; `chunk` = size: query i
+sees key j <= i only if floor(i / size) = floor(j / size), counted from the sequence's position 0 (the cache
+then keeps the pages of the query's own run alone); `fixed_sink` = s: a sink whose score is the constant s.
 """
 from __future__ import annotations
 
-from .base import CacheNeed, Mixer, WeightSpec, register_part
+from .base import CacheNeed, Mixer, StateNeed, WeightSpec, register_part
+
+
+def slope_base_or_sink(slope_base, sink) -> bool:
+    return slope_base is not None or sink is not None
 
 
 class CausalAttention(Mixer):
@@ -38,7 +52,8 @@ class CausalAttention(Mixer):
                  bias: bool = True, init_std: float = 0.02, out_init_std: float = 0.02, bias_init_std: float = 0.01,
                  keep_first: int = 0, value_dim: int | None = None, suffix: str = ".weight", qk_norm=None,
                  value_norm: bool = False, norm_eps: float = 0.0, q_temp=None, distance_slope_base: float | None = None,
-                 sink: str | None = None, gate: str | None = None):
+                 sink: str | None = None, gate: str | None = None, qkv_bias: str | None = None, conv=None, rotary=None,
+                 head_scale: str | None = None, chunk: int = 0, fixed_sink: float | None = None):
         super().__init__(prefix)
         if n_heads % kv_heads:
             raise ValueError(f"attention {prefix!r}: {n_heads} heads are not a multiple of {kv_heads} key/value heads")
@@ -59,8 +74,29 @@ class CausalAttention(Mixer):
         self.gate_name = None if gate is None else prefix + gate
         # rows that pass a norm, a temperature or a gate between the projection and the attention
         self.prepared = self.qk_norm_names is not None or self.value_norm or self.q_temp is not None or self.gate_name is not None
-        self.biased = self.slope_base is not None or self.sink_name is not None
-        if (self.prepared or self.biased) and bias:
+        self.fixed_sink = None if fixed_sink is None else float(fixed_sink)
+        self.chunk = int(chunk)
+        self.head_scale_name = None if head_scale is None else prefix + head_scale
+        self.conv = None if conv is None else (int(conv[0]), str(conv[1]))
+        self.qkv_bias_suffix = qkv_bias
+        self.rotary = None
+        if rotary is not None:
+            from .position import Rotary
+            self.rotary = Rotary(prefix, dims=int(rotary[0]), base=float(rotary[1]), interleaved=bool(rotary[2]))
+            if self.rotary.dims > head_dim:
+                raise ValueError(f"attention {prefix!r}: {self.rotary.dims} rotated dimensions of a head of {head_dim}")
+        if self.chunk < 0 or (self.chunk and window):
+            raise ValueError(f"attention {prefix!r}: chunk {self.chunk} (not negative, and not beside a window)")
+        if self.fixed_sink is not None and sink is not None:
+            raise ValueError(f"attention {prefix!r}: a learned sink or a fixed one")
+        if self.conv is not None and not 1 <= self.conv[0] <= 16:
+            raise ValueError(f"attention {prefix!r}: a convolution of {self.conv[0]} taps is not in [1, 16]")
+        if (qkv_bias is not None or self.conv is not None) and (isinstance(qkv, str) or bias):
+            raise ValueError(f"attention {prefix!r}: biases on q, k and v alone and convolutions come with q, k and v "
+                             "stored as three matrices, without the fused projection's biases")
+        self.biased = (self.slope_base is not None or self.sink_name is not None or self.fixed_sink is not None
+                       or self.chunk > 0 or self.head_scale_name is not None)
+        if (self.prepared or slope_base_or_sink(distance_slope_base, sink)) and bias:
             raise ValueError(f"attention {prefix!r}: norms, gates, slopes and sinks come without biases")
         self.extended = int(keep_first) > 0 or value_dim is not None or self.prepared or self.biased
         self.value_dim = self.head_dim if value_dim is None else int(value_dim)
@@ -101,6 +137,12 @@ class CausalAttention(Mixer):
             specs.append(WeightSpec(self.sink_name, (self.n_heads,), std=1.0))
         if self.gate_name is not None:
             specs.append(WeightSpec(self.gate_name + self.suffix, self._shape(self.width, self.o_width), std=self.init_std))
+        if self.qkv_bias_suffix is not None:
+            specs += [WeightSpec(n + self.qkv_bias_suffix, (w,), std=self.bias_init_std * 10) for n, w in zip(self.qkv_name, self.widths)]
+        if self.conv is not None:
+            specs += [WeightSpec(n + self.conv[1], (w, self.conv[0]), std=0.5) for n, w in zip(self.qkv_name, self.widths)]
+        if self.head_scale_name is not None:
+            specs.append(WeightSpec(self.head_scale_name, (self.n_heads,), mean=1.0, std=0.2))
         return specs
 
     def load(self, get, runtime):
@@ -130,11 +172,34 @@ class CausalAttention(Mixer):
         if self.bias:
             self.b_qkv = runtime.vector(get(self.qkv_name + ".bias"))
             self.b_out = runtime.vector(get(self.out_name + ".bias"))
+        if self.qkv_bias_suffix is not None:
+            self.b_qkv = torch.cat([runtime.vector(get(n + self.qkv_bias_suffix)) for n in self.qkv_name]).contiguous()
+        if self.conv is not None:
+            self.conv_w = torch.cat([runtime.vector(get(n + self.conv[1])) for n in self.qkv_name]).contiguous()
+            self.conv_b = torch.zeros(self.qkv_width, dtype=torch.float32, device=self.conv_w.device)
+        if self.rotary is not None:
+            self.rotary.load(get, runtime)
+        if self.fixed_sink is not None:
+            self.sinks = torch.full((self.n_heads,), self.fixed_sink, dtype=torch.float32, device=self.w_qkv.device)
+        self.head_scales = None
+        if self.head_scale_name is not None:
+            self.head_scales = runtime.vector(get(self.head_scale_name))
+            # (the tensor-core kernels take their exponents against a running maximum of the raw products, which
+            # needs factors above zero; any other head takes the plain kernel)
+            self.head_scales_positive = bool((self.head_scales > 0).all())
 
     def stream_weights(self):
         return [self.w_qkv, self.w_out]
 
+    def state_need(self):
+        if self.conv is None or self.conv[0] <= 1:
+            return None
+        return {"conv": StateNeed((self.conv[0] - 1, self.qkv_width))}     # the projected rows before the step's first, oldest first
+
     def cache_need(self):
+        if self.chunk > 0:
+            return CacheNeed("chunk", self.kv_heads, self.head_dim, self.chunk, 0,
+                             0 if self.value_dim == self.head_dim else self.value_dim)
         windowed = self.window > 0
         return CacheNeed("window" if windowed else "full", self.kv_heads, self.head_dim, self.window,
                          self.keep_first if windowed else 0, 0 if self.value_dim == self.head_dim else self.value_dim)
@@ -154,7 +219,17 @@ class CausalAttention(Mixer):
                               value_dim=self.value_dim, slopes=self.slopes, sinks=self.sinks)
             return o if self.gate_name is None else ops.gate_mul(o, proj, self.gate_col, "sigmoid")
         qkv = ops.linear(h, self.w_qkv, self.b_qkv, out_dtype=ctx.dtype)
+        if self.conv is not None:
+            state = app.state.get("conv") if isinstance(app.state, dict) else None
+            qkv = ops.conv_silu(qkv, 0, self.qkv_width, self.conv_w, self.conv_b, state, ctx.plan, act="none")
         ctx.position.apply_qk(ctx, qkv, self.n_heads, self.kv_heads, self.head_dim)
+        if self.rotary is not None:
+            self.rotary.apply_qk(ctx, qkv, self.n_heads, self.kv_heads, self.head_dim)
+        if self.chunk > 0 or self.head_scales is not None:
+            return ops.attention(qkv, app.cache, ctx.plan, self.n_heads, self.kv_heads, self.head_dim, self.scale,
+                                 self.window, out_dtype=ctx.dtype, store=app.writes_cache, keep_first=0, value_dim=self.value_dim,
+                                 slopes=self.slopes, sinks=self.sinks, chunk=self.chunk, head_scales=self.head_scales,
+                                 head_scales_positive=self.head_scales is None or self.head_scales_positive)
         if not self.extended:
             return ops.attention(qkv, app.cache, ctx.plan, self.n_heads, self.kv_heads, self.head_dim, self.scale,
                                  self.window, out_dtype=ctx.dtype, store=app.writes_cache)

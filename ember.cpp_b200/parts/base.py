@@ -19,7 +19,9 @@ Roles and what each must provide:
             carries per sequence, kept by the cache beside the layers' states)
   position  embedding_table() -> tensor | None, max_positions() -> int | None,
             apply_qk(ctx, qkv, n_heads, kv_heads, head_dim) (in place; default: nothing)
-  block     forward(ctx, x, app) -> x       (the arrangement of the four parts above)
+  addon     forward(ctx, x) -> x            (something added to the stream after a layer's sublayers, reading the
+            stream itself and, where it sets `needs_tokens`, the step's token ids)
+  block     forward(ctx, x, app) -> x       (the arrangement of the parts above)
 
 Every part lists its tensors with `weight_specs()` (name, stored shape, how random-weights mode
 fills it) and receives them in `load(get, runtime)`.
@@ -42,14 +44,17 @@ class WeightSpec:
     std: float = 0.02
     integer: bool = False     # an integer table (kept as int32); none in GPT-2
     below: int = 0            # integer tables in random-weights mode: every row holds distinct values of [0, below)
+    free: tuple[int, ...] = ()  # dimensions whose size the checkpoint gives (a rank that no configuration key names);
+                                # `shape` holds there the size that random-weights mode draws
 
 
 @dataclasses.dataclass(frozen=True)
 class CacheNeed:
-    """What a mixer wants from the cache: all keys (`full`) or the last `window` of them, with
-    the first `keep_first` positions of the sequence kept beside the window for good.  Values may
+    """What a mixer wants from the cache: all keys (`full`), the last `window` of them (`window`), with
+    the first `keep_first` positions of the sequence kept beside the window for good, or the keys of
+    the query's own run of `window` positions counted from the sequence's start (`chunk`).  Values may
     have a row size of their own (`value_dim`; 0: the keys')."""
-    kind: str                 # "full" | "window"
+    kind: str                 # "full" | "window" | "chunk"
     kv_heads: int
     head_dim: int
     window: int = 0
@@ -172,6 +177,16 @@ class EmbedPart(Part):
         raise NotImplementedError
 
 
+class StreamAddon(Part):
+    """Something a layer adds to the residual stream after its sublayers (a per-layer input taken from the
+    token ids, for instance).  It reads the float32 stream and returns the new one."""
+    role = "addon"
+    needs_tokens = False
+
+    def forward(self, ctx, x):
+        raise NotImplementedError
+
+
 class Position(Part):
     role = "position"
 
@@ -192,15 +207,21 @@ class Block(Part):
         super().__init__("")
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
         self.more_norms = dict(more_norms)     # the arrangement's further norms, by the names the spec gives them
+        self.addons: list = []                 # what the layer adds to the stream after its sublayers (set by the model)
 
     def parts(self):
-        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn, *self.more_norms.values()) if p is not None]
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn, *self.more_norms.values(), *self.addons) if p is not None]
+
+    def add_ons(self, ctx, x):
+        for part in self.addons:
+            x = part.forward(ctx, x)
+        return x
 
     def forward(self, ctx, x, app):
         raise NotImplementedError
 
 
-_REGISTRY: dict[str, dict[str, Callable[..., Part]]] = {r: {} for r in ("norm", "mixer", "ffn", "position", "block", "embed")}
+_REGISTRY: dict[str, dict[str, Callable[..., Part]]] = {r: {} for r in ("norm", "mixer", "ffn", "position", "block", "embed", "addon")}
 
 
 def register_part(role: str, kind: str, factory: Callable[..., Part]) -> None:

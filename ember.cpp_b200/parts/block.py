@@ -3,7 +3,9 @@
 `pre_norm` is GPT-2's: `x -> norm1 -> mixer -> +x -> norm2 -> feed-forward -> +x`, the residual
 sums in float32 (graph_ir.cpp:732-756, the sequential branch; operand order x then the
 branch's output, :754-756).  The mixer and the feed-forward add into the stream themselves so that
-their last projection can do the sum in its epilogue.
+their last projection can do the sum in its epilogue.  A layer of this arrangement may have no
+feed-forward (and then no second norm), and may add further things to the stream after its sublayers
+(`LayerSpec.addons`).
 
 `sandwich` norms every sublayer on both sides: `x -> x + after_mixer(mixer(norm1(x)))`, then
 `x -> x + after_ffn(ffn(norm2(x)))`.  A sublayer's output cannot be added by its last projection
@@ -22,21 +24,22 @@ from .base import Block, register_part
 
 class PreNormBlock(Block):
     def __init__(self, norm1, mixer, norm2, ffn, **more_norms):
-        if norm1 is None or norm2 is None or more_norms:
-            raise ValueError("block 'pre_norm' has exactly two norms: one before the mixer, one before the feed-forward")
-        if ffn is None:
-            raise ValueError("block 'pre_norm' has a feed-forward")
+        if norm1 is None or more_norms or (ffn is None) != (norm2 is None):
+            raise ValueError("block 'pre_norm' has a norm before the mixer and, with a feed-forward, one before that")
         super().__init__(norm1, mixer, norm2, ffn)
 
 
     def forward(self, ctx, x, app):
         announce = getattr(ctx.ops, "announce_weights", None)
         if announce is not None:    # a hint: this block's matrices in the order they are streamed, then what follows
-            announce(self.mixer.stream_weights() + self.ffn.stream_weights() + list(getattr(ctx, "next_weights", ())))
+            announce(self.mixer.stream_weights() + (self.ffn.stream_weights() if self.ffn is not None else [])
+                     + list(getattr(ctx, "next_weights", ())))
         h = self.norm1.forward(ctx, x, ctx.dtype)
         x = self.mixer.forward(ctx, h, x, app)
-        h = self.norm2.forward(ctx, x, ctx.dtype)
-        return self.ffn.forward(ctx, h, x)
+        if self.ffn is not None:
+            h = self.norm2.forward(ctx, x, ctx.dtype)
+            x = self.ffn.forward(ctx, h, x)
+        return self.add_ons(ctx, x)
 
 
 class SandwichBlock(Block):

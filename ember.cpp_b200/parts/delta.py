@@ -105,3 +105,92 @@ class GatedDeltaRule(Mixer):
 
 
 register_part("mixer", "gated_delta_rule", GatedDeltaRule)
+
+
+class GeneralizedDeltaRule(Mixer):
+    """The delta rule with a decay and a removal rate for every key channel (the state update of RWKV-7:
+    Peng et al., "RWKV-7 'Goose' with Expressive Dynamic State Evolution").
+
+    Per head r = W_r h, k = W_k h, v = W_v h (dim values each), a decay
+    w = exp(-decay_coef * sigmoid(W_w2 tanh(W_w1 h) + w0)) and a removal rate a = sigmoid(W_a h + b_a) for
+    every key channel.  With the unit key u = k / sqrt(sum k^2 + 1e-6) and a state S of dim x dim float32
+    values that starts at zero:
+
+        S_t = diag(w_t) S_(t-1) - (a_t * u_t)(u_t^T S_(t-1)) + k_t v_t^T        o_t = S_t^T r_t
+
+    both of the first two terms reading the state of the token before.  Each head's o is divided by its
+    root mean square, the heads laid end to end are multiplied by a gain of that whole size and by
+    sigmoid(W_g h), and projected out.  The decay's second product, the decays and rates, the unit keys,
+    the recurrence and its state, and the norm are float32 in every mode; r | k | v | g | a | w1 are one
+    product in the compute type.  What a sequence carries: S of every head (`StateNeed` "S")."""
+
+    def __init__(self, prefix: str, width: int, heads: int, dim: int, eps: float, decay_coef: float,
+                 r: str = "r", k: str = "k", v: str = "v", gate: str = "g", rate: str = "a", decay_in: str = "w1",
+                 decay_out: str = "w2", decay_bias: str = "w0", bias_suffix: str = ".b", norm: str = "norm", out: str = "o",
+                 rank: int = 16, init_std: float = 0.02, out_init_std: float = 0.02):
+        """rank: of the decay's two-step product in random-weights mode; a checkpoint's tensors give their own."""
+        super().__init__(prefix)
+        self.width, self.heads, self.dim = int(width), int(heads), int(dim)
+        self.eps, self.decay_coef, self.rank = float(eps), float(decay_coef), int(rank)
+        if self.heads <= 0 or not 1 <= self.dim <= 256:
+            raise ValueError(f"generalized delta rule {prefix!r}: {self.heads} heads of {self.dim} (head size in [1, 256])")
+        self.inner = self.heads * self.dim
+        self.names = {n: prefix + s for n, s in dict(r=r, k=k, v=v, gate=gate, a=rate, w1=decay_in, w2=decay_out,
+                                                     w0=decay_bias, norm=norm, out=out).items()}
+        self.bias_suffix = bias_suffix
+        self.init_std, self.out_init_std = init_std, out_init_std
+        self.w_in = self.w_out = None
+
+    def weight_specs(self):
+        n, d, m = self.names, self.width, self.inner
+        return [WeightSpec(n[key], (m, d), std=self.init_std) for key in ("r", "k", "v", "gate", "a")] + [
+            WeightSpec(n["a"] + self.bias_suffix, (m,), std=1.0),
+            WeightSpec(n["w1"], (self.rank, d), std=self.init_std, free=(0,)),
+            WeightSpec(n["w2"], (m, self.rank), std=0.5, free=(1,)),
+            WeightSpec(n["w0"], (m,), std=1.0),
+            WeightSpec(n["norm"], (m,), mean=1.0, std=0.1),
+            WeightSpec(n["out"], (d, m), std=self.out_init_std)]
+
+    def load(self, get, runtime):
+        import torch
+        n = self.names
+        parts = [runtime.matrix(get(n[key])) for key in ("r", "k", "v", "gate", "a", "w1")]
+        self.rank = parts[-1].shape[0]
+        if self.rank > 256 or get(n["w2"]).shape[1] != self.rank:
+            raise ValueError(f"generalized delta rule {self.prefix!r}: the decay's two matrices meet in {self.rank} and "
+                             f"{get(n['w2']).shape[1]} values (one rank of at most 256)")
+        w = torch.cat(parts)
+        pad = -w.shape[0] % 8      # rows of zeros: every row of the projection's output starts on 16 bytes
+        if pad:
+            w = torch.cat([w, torch.zeros((pad, self.width), dtype=w.dtype, device=w.device)])
+        self.w_in = w.contiguous()
+        self.w_out = runtime.matrix(get(n["out"]))
+        self.w_w2 = runtime.vector(get(n["w2"]))                   # float32 [heads * dim, rank]
+        self.w0 = runtime.vector(get(n["w0"]))
+        self.b_a = runtime.vector(get(n["a"] + self.bias_suffix))
+        self.norm_w = runtime.vector(get(n["norm"]))
+
+    def stream_weights(self):
+        return [self.w_in, self.w_out]
+
+    def state_need(self):
+        return {"S": StateNeed((self.heads, self.dim, self.dim))}
+
+    def _mix(self, ctx, h, app):
+        ops, m = ctx.ops, self.inner
+        proj = ops.linear(h, self.w_in, None, out_dtype=ctx.dtype)                    # [T, r | k | v | g | a | w1 (| 0)]
+        wz = ops.low_rank_out(proj, 5 * m, self.w_w2, self.w0, "tanh")                # float32 [T, heads * dim]
+        o = ops.generalized_delta_rule(proj, 0, m, 2 * m, 4 * m, self.b_a, wz, self.decay_coef, app.state["S"], ctx.plan,
+                                       self.heads, self.dim, UNIT_EPS)
+        return ops.gated_group_norm(o, proj, 3 * m, self.norm_w, self.heads, self.eps, ctx.dtype, gate_first=False,
+                                    gate="sigmoid")
+
+    def forward(self, ctx, h, residual, app):
+        return ctx.ops.linear(self._mix(ctx, h, app), self.w_out, None, residual=residual)
+
+    def branches(self, ctx, h, app):
+        import torch
+        return [(ctx.ops.linear(self._mix(ctx, h, app), self.w_out, None, out_dtype=torch.float32), 1.0)]
+
+
+register_part("mixer", "generalized_delta_rule", GeneralizedDeltaRule)

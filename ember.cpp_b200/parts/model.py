@@ -26,6 +26,7 @@ class DecoderModel:
             norm = lambda part: None if part is None else build_part("norm", part)  # noqa: E731
             self.blocks.append(build_block(layer.block, norm(layer.norm1), build_part("mixer", layer.mixer), norm(layer.norm2),
                                            None if layer.ffn is None else build_part("ffn", layer.ffn), {name: norm(part) for name, part in layer.more_norms}))
+            self.blocks[-1].addons = [build_part("addon", part) for part in layer.addons]
         self.final_norm = build_part("norm", spec.final_norm)
         self.embed_parts = [build_part("embed", part) for part in spec.embed_parts]
         self.embed_norm = None if spec.embed_norm is None else build_part("norm", spec.embed_norm)

@@ -13,8 +13,9 @@ Fan, Shippole, "YaRN: Efficient Context Window Extension of Large Language Model
 of pair i is a blend of f_i / factor and f_i by a ramp over the pair index, the ramp's ends being
 the indices whose wavelengths make `fast` and `slow` turns within the `original` context, and both
 cos and sin are multiplied by 0.1 ln(factor) + 1.  Frequencies are computed once on the host, the
-angles and their cos and sin in float32 on the device.  A mixer that rotates only a part of its
-heads builds one of these for itself and calls `rotate`.
+angles and their cos and sin in float32 on the device.  With `interleaved` the pairs are neighbours:
+dimension 2i with dimension 2i + 1.  A mixer that rotates only a part of its heads, or with constants
+of its own, builds one of these for itself and calls `rotate`.
 """
 from __future__ import annotations
 
@@ -51,10 +52,11 @@ class NoPosition(Position):
 
 class Rotary(Position):
 
-    def __init__(self, prefix: str = "", dims: int = 0, base: float = 10000.0, scaling: dict | None = None):
+    def __init__(self, prefix: str = "", dims: int = 0, base: float = 10000.0, scaling: dict | None = None,
+                 interleaved: bool = False):
         super().__init__(prefix)
         import math
-        self.dims, self.base = int(dims), float(base)
+        self.dims, self.base, self.interleaved = int(dims), float(base), bool(interleaved)
         if self.dims <= 0 or self.dims % 2:
             raise ValueError(f"rotary {prefix!r}: {self.dims} rotated dimensions (an even number)")
         half = self.dims // 2
@@ -82,7 +84,7 @@ class Rotary(Position):
         """dst[t, dst_col + h * dst_head + (0..width)] = the rotated src[t, src_col + h * src_head + (0..width)] for
         h < heads, by each token's position; src and dst may be one tensor (in place)."""
         return ctx.ops.rotate(src, dst, ctx.plan.positions, heads, src_col, src_head, dst_col, dst_head, width,
-                              self.freqs, self.magnitude, self.dims)
+                              self.freqs, self.magnitude, self.dims, **({"interleaved": True} if self.interleaved else {}))
 
     def apply_qk(self, ctx, qkv, n_heads: int, kv_heads: int, head_dim: int) -> None:
         self.rotate(ctx, qkv, qkv, n_heads + kv_heads, 0, head_dim, 0, head_dim, head_dim)

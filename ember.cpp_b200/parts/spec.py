@@ -29,13 +29,15 @@ class LayerSpec:
     the residual stream are wired).  An arrangement with one shared norm leaves `norm2` None; one
     with more norms than two (norms after the mixer and after the feed-forward as well) names the
     others in `more_norms`, and its block receives them as keyword arguments of those names.  A
-    layer without a feed-forward leaves `ffn` None (its arrangement must allow that)."""
+    layer without a feed-forward leaves `ffn` None (its arrangement must allow that).  `addons` are parts
+    of the `addon` role that the layer applies to the stream after its sublayers, in order."""
     block: str
     norm1: PartSpec | None
     mixer: PartSpec
     norm2: PartSpec | None
     ffn: PartSpec | None
     more_norms: tuple[tuple[str, PartSpec], ...] = ()
+    addons: tuple[PartSpec, ...] = ()
 
 
 @dataclasses.dataclass(frozen=True)

@@ -51,8 +51,10 @@ def check_tensors(where: str, tensors: dict[str, torch.Tensor], specs: list[Weig
     missing = [n for n in want if n not in have]
     patterns = [re.compile(p) for p in ignored]
     unexpected = [n for n in have if n not in want and not any(p.fullmatch(n) for p in patterns)]
+    def fits(spec, got):       # (a dimension that the specification leaves free takes the checkpoint's size)
+        return len(got) == len(spec.shape) and all(a == b or i in spec.free for i, (a, b) in enumerate(zip(spec.shape, got)))
     wrong_shape = [(n, want[n].shape, tuple(have[n].shape)) for n in want
-                   if n in have and tuple(have[n].shape) != tuple(want[n].shape)]
+                   if n in have and not fits(want[n], tuple(have[n].shape))]
     wrong_type = []
     for n, s in want.items():
         if n in have and isinstance(have[n], UnreadTensor):

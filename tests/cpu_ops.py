@@ -67,7 +67,7 @@ class CpuOps:
             cache.v[page, :, p % PAGE, :] = qkv[t, q_w + kv_w:q_w + kv_w + kv_heads * vd].view(kv_heads, vd).to(cache.v.dtype)
 
     def attention(self, qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype, store=False,
-                  keep_first=0, value_dim=None, slopes=None, sinks=None):
+                  keep_first=0, value_dim=None, slopes=None, sinks=None, chunk=0, head_scales=None, head_scales_positive=True):
         keep_first = keep_first or 0
         if store:
             self.kv_store(qkv, cache, plan, n_heads, kv_heads, head_dim, value_dim)
@@ -81,6 +81,8 @@ class CpuOps:
                 continue
             p = int(plan.positions[t])
             lo = max(0, p - window + 1) if window > 0 else 0
+            if chunk > 0:
+                lo = p // chunk * chunk
             pos = torch.arange(lo, p + 1)
             if window > 0 and keep_first > 0 and lo > 0:
                 pos = torch.cat([torch.arange(0, min(keep_first, lo)), pos])
@@ -90,7 +92,7 @@ class CpuOps:
             v = cache.v[pages, :, pos % PAGE, :].float()
             q = qkv[t, :n_heads * head_dim].float().view(n_heads, head_dim)
             for h in range(n_heads):
-                sc = (k[:, h // rep, :] @ q[h]) * scale
+                sc = (k[:, h // rep, :] @ q[h]) * scale * (1.0 if head_scales is None else float(head_scales[h]))
                 if slopes is not None:
                     sc = sc - slopes[h] * (p - pos).float()
                 if sinks is not None:       # one more term of the denominator, without a value
@@ -129,7 +131,7 @@ class CpuOps:
         slots, starts, cu = plan.seq_slot.tolist(), plan.seq_start.tolist(), plan.cu_new.tolist()
         return [(slots[i], starts[i], cu[i], cu[i + 1]) for i in range(plan.n)]
 
-    def conv_silu(self, proj, col0, channels, conv_w, conv_b, conv_state, plan):
+    def conv_silu(self, proj, col0, channels, conv_w, conv_b, conv_state, plan, act="silu"):
         taps = conv_w.shape[1]
         out = torch.zeros(proj.shape[0], channels)
         for slot, start, t0, t1 in self._sequences(plan):
@@ -143,7 +145,7 @@ class CpuOps:
             acc = conv_b.clone().expand(t1 - t0, channels).clone()
             for j in range(taps):
                 acc += conv_w[:, j] * u[j:j + t1 - t0]
-            out[t0:t1] = acc * torch.sigmoid(acc)
+            out[t0:t1] = acc * torch.sigmoid(acc) if act == "silu" else acc
         return out.to(proj.dtype)
 
     def ssd_scan(self, xbc, proj, dt_col, dt_bias, a_log, skip, state, plan, heads, vdim, groups, n_state):
@@ -267,14 +269,20 @@ class CpuOps:
         return x
 
     # ------------------------------------------------------------------ rotation, rows of low rank, products per head
-    def rotate(self, src, dst, positions, heads, src_col, src_head, dst_col, dst_head, width, freqs, magnitude, dims):
+    def rotate(self, src, dst, positions, heads, src_col, src_head, dst_col, dst_head, width, freqs, magnitude, dims,
+               interleaved=False):
         half = dims // 2
         a = positions.double()[:, None] * freqs.double()[None, :]
         c, s = (torch.cos(a) * magnitude).float(), (torch.sin(a) * magnitude).float()
         for h in range(heads):
             x = src[:, src_col + h * src_head: src_col + h * src_head + width].float()
-            u, v = x[:, :half], x[:, half:dims]
-            y = torch.cat([u * c - v * s, v * c + u * s, x[:, dims:]], 1)
+            if interleaved:
+                u, v = x[:, 0:dims:2], x[:, 1:dims:2]
+                y = x.clone()
+                y[:, 0:dims:2], y[:, 1:dims:2] = u * c - v * s, v * c + u * s
+            else:
+                u, v = x[:, :half], x[:, half:dims]
+                y = torch.cat([u * c - v * s, v * c + u * s, x[:, dims:]], 1)
             dst[:, dst_col + h * dst_head: dst_col + h * dst_head + width] = y.to(dst.dtype)
         return dst
 
@@ -347,17 +355,104 @@ class CpuOps:
 
     # ------------------------------------------------------------------ experts by table
     def moe_route(self, tokens, T, table, experts, top):
+        if tokens is None:                                # the table's row t is token t's choice
+            return table[:T].long()
         return table[tokens[:T].long()].long()            # [T, top]: the expert of every (token, choice) pair
 
-    def moe_gate_up(self, h, w_gate_up, routing, out_dtype):
+    def moe_pick(self, logits, correction, experts, top, groups, keep_groups, route_scale):
+        s = torch.sigmoid(logits[:, :experts].float())
+        choice = s + correction
+        per = experts // groups
+        if groups > 1:
+            grouped = choice.view(-1, groups, per)
+            score = grouped.topk(min(2, per), dim=-1).values.sum(-1)
+            kept = score.topk(keep_groups, dim=-1).indices
+            allowed = torch.zeros_like(score, dtype=torch.bool).scatter_(1, kept, True)
+            choice = torch.where(allowed.repeat_interleave(per, dim=1), choice, torch.full_like(choice, -float("inf")))
+        chosen = choice.topk(top, dim=-1).indices
+        w = s.gather(1, chosen)
+        return chosen.to(torch.int32), w / (w.sum(-1, keepdim=True) + 1e-20) * route_scale
+
+    def moe_combine(self, x, y, weights, shared, logits, gate_col):
+        out = x + (y * weights[:, :, None]).sum(1)
+        if shared is not None:
+            out = out + (shared if logits is None else shared * torch.sigmoid(logits[:, gate_col:gate_col + 1].float()))
+        return out
+
+    def moe_gate_up(self, h, w_gate_up, routing, out_dtype, limit=0.0, alpha=1.0, shift=0.0):
         T, top = routing.shape
         n = w_gate_up.shape[1] // 2
         out = torch.zeros(T * top, n)
         for t in range(T):
             for k in range(top):
                 gu = w_gate_up[routing[t, k]].float() @ h[t].float()
-                out[t * top + k] = gu[:n] * torch.sigmoid(gu[:n]) * gu[n:]
+                g, u = gu[:n], gu[n:]
+                if limit > 0:
+                    g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+                    out[t * top + k] = g * torch.sigmoid(alpha * g) * (u + shift)
+                else:
+                    out[t * top + k] = g * torch.sigmoid(g) * u
         return out.to(out_dtype)
+
+    # ------------------------------------------------------------------ token shift, linear attention, the generalized delta rule
+    def token_shift(self, h, mu, state, plan):
+        out = torch.zeros_like(h, dtype=torch.float32)
+        for slot, start, t0, t1 in self._sequences(plan):
+            if slot < 0:
+                continue
+            rows = h[t0:t1].float()
+            before = state[slot].clone() if start > 0 else torch.zeros_like(rows[0])
+            prev = torch.cat([before[None], rows[:-1]])
+            out[t0:t1] = rows + (prev - rows) * mu
+            state[slot] = rows[-1]
+        return out.to(h.dtype)
+
+    def low_rank_out(self, proj, col, w2, bias, act):
+        lr = proj[:, col:col + w2.shape[1]].float()
+        if act == "tanh":
+            lr = torch.tanh(lr)
+        return lr @ w2.t() + bias
+
+    def gla_scan(self, proj, q_col, k_col, v_col, z, tau, state, plan, heads, dim, vdim):
+        out = torch.zeros(proj.shape[0], heads * vdim)
+        alpha = torch.exp(torch.nn.functional.logsigmoid(z.float()) / tau)
+        for slot, start, t0, t1 in self._sequences(plan):
+            if slot < 0:
+                continue
+            S = state[slot].clone() if start > 0 else torch.zeros(heads, dim, vdim)
+            for t in range(t0, t1):
+                q = proj[t, q_col:q_col + heads * dim].float().view(heads, dim) * dim ** -0.5
+                k = proj[t, k_col:k_col + heads * dim].float().view(heads, dim)
+                v = proj[t, v_col:v_col + heads * vdim].float().view(heads, vdim)
+                S = alpha[t].view(heads, dim)[:, :, None] * S + k[:, :, None] * v[:, None, :]
+                out[t] = torch.einsum("hdv,hd->hv", S, q).reshape(-1)
+            state[slot] = S
+        return out
+
+    def generalized_delta_rule(self, proj, r_col, k_col, v_col, a_col, a_bias, wz, decay_coef, state, plan, heads, dim, unit_eps):
+        m = heads * dim
+        out = torch.zeros(proj.shape[0], m)
+        w_all = torch.exp(-decay_coef * torch.sigmoid(wz.float()))
+        for slot, start, t0, t1 in self._sequences(plan):
+            if slot < 0:
+                continue
+            S = state[slot].clone() if start > 0 else torch.zeros(heads, dim, dim)
+            for t in range(t0, t1):
+                r, k, v = (proj[t, c:c + m].float().view(heads, dim) for c in (r_col, k_col, v_col))
+                a = torch.sigmoid(proj[t, a_col:a_col + m].float() + a_bias).view(heads, dim)
+                u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)
+                uS = torch.einsum("hd,hdv->hv", u, S)
+                S = w_all[t].view(heads, dim)[:, :, None] * S - (a * u)[:, :, None] * uS[:, None, :] + k[:, :, None] * v[:, None, :]
+                out[t] = torch.einsum("hdv,hd->hv", S, r).reshape(-1)
+            state[slot] = S
+        return out
+
+    def side_input(self, x, plan, table, col, dim, w_gate, w_proj, w_norm, eps):
+        e = table[plan.tokens[:x.shape[0]].long(), col:col + dim].float()
+        z = x.float() @ w_gate.float().t()
+        g = 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3))) * e
+        y = g @ w_proj.float().t()
+        return x + y * torch.rsqrt((y * y).mean(-1, keepdim=True) + eps) * w_norm
 
     def moe_down(self, inner, w_down, routing):
         T, top = routing.shape

@@ -503,7 +503,7 @@ def test_other_arrangements_states_and_model_options(ops, dtype):
             assert rel_error(got, plain(ids)) < tol
         eng.cache.check()
         assert eng.cache.slots.held == 0
-    with pytest.raises(ValueError, match="exactly two norms"):       # GPT-2's arrangement says what it needs
+    with pytest.raises(ValueError, match="a norm before the mixer"):       # GPT-2's arrangement says what it needs
         DecoderModel(ModelSpec(width=width, vocab_size=vocab, token_table="embed.weight", position=spec.position,
                                layers=(LayerSpec("pre_norm", ln("a."), attn, None, dense("b.")),), schedule=(Application(0),),
                                final_norm=ln("norm."), head=None))
