@@ -25,7 +25,8 @@ decode_kept_partial_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfl
                            const __nv_bfloat16* __restrict__ vc, float* __restrict__ part,
                            const int* __restrict__ positions, const int* __restrict__ seq_slot,
                            const int* __restrict__ pages, int max_blocks, int n_heads, int kv_heads, int hd, int vd,
-                           float scale, int window, int keep_first, int n_chunks, const float* __restrict__ slopes) {
+                           float scale, int window, int keep_first, int n_chunks, const float* __restrict__ slopes, int chunk,
+                           const float* __restrict__ head_scales) {
   __shared__ float q_s[PER][256];
   __shared__ float m_s[kWarps][PER], l_s[kWarps][PER];
   __shared__ float acc_s[kWarps][PER][32 * DPL];
@@ -34,7 +35,8 @@ decode_kept_partial_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfl
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = seq_slot[t];
   const int p = positions[t];
-  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  // the first visible key: the window's, or (chunk > 0) the first position of the query's own run of `chunk` positions
+  const int lo = chunk > 0 ? p / chunk * chunk : (window > 0 ? max(0, p - window + 1) : 0);
   const int n_kept = window > 0 ? min(keep_first, lo) : 0;
   const int n_keys = n_kept + p - lo + 1;
   const int k0 = c * kChunkKeys;
@@ -88,7 +90,8 @@ decode_kept_partial_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfl
 #pragma unroll
   for (int h = 0; h < PER; ++h) {
     const float slope = slopes && h < per ? slopes[g * per + h] : 0.f;
-    const float s = valid ? sc[h] * scale - slope * (float)(p - j) : -INFINITY;
+    const float hs = head_scales && h < per ? scale * head_scales[g * per + h] : scale;
+    const float s = valid ? sc[h] * hs - slope * (float)(p - j) : -INFINITY;
     const float m = warp_max(s);  // (the warp's first key is always there: m is finite)
     pj[h] = valid ? expf(s - m) : 0.f;
     const float l = warp_sum(pj[h]);
@@ -199,10 +202,11 @@ __global__ void decode_kept_merge_kernel(const float* __restrict__ part, __nv_bf
 template <int PER, int DPL>
 void launch_partial(dim3 grid, cudaStream_t stream, const void* qkv, const void* kc, const void* vc, float* part,
                     const int* positions, const int* seq_slot, const int* pages, int max_blocks, int n_heads,
-                    int kv_heads, int hd, int vd, float scale, int window, int keep_first, int n_chunks, const float* slopes) {
+                    int kv_heads, int hd, int vd, float scale, int window, int keep_first, int n_chunks, const float* slopes,
+                    int chunk, const float* head_scales) {
   launch_plain(decode_kept_partial_kernel<PER, DPL>, grid, dim3(32 * kWarps), 0, stream, (const __nv_bfloat16*)qkv,
              (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, part, positions, seq_slot, pages, max_blocks, n_heads,
-             kv_heads, hd, vd, scale, window, keep_first, n_chunks, slopes);
+             kv_heads, hd, vd, scale, window, keep_first, n_chunks, slopes, chunk, head_scales);
 }
 
 }  // namespace
@@ -234,11 +238,30 @@ EMBER_API int ember_attention_decode_kept(const void* qkv, const void* kc, const
 
 // The same with a distance penalty (slopes: float32 per query head, or null) and a sink in the softmax's denominator
 // (sinks: float32 per query head, or null).
+EMBER_API int ember_attention_decode_chunked(const void* qkv, const void* kc, const void* vc, void* out, float* scratch,
+                                             const int* positions, const int* seq_slot, const int* pages, int max_blocks,
+                                             int T, int n_heads, int kv_heads, int hd, int vd, float scale, int window,
+                                             int keep_first, int max_keys, const float* slopes, const float* sinks, int chunk,
+                                             const float* head_scales, cudaStream_t stream);
+
 EMBER_API int ember_attention_decode_biased(const void* qkv, const void* kc, const void* vc, void* out, float* scratch,
                                             const int* positions, const int* seq_slot, const int* pages, int max_blocks,
                                             int T, int n_heads, int kv_heads, int hd, int vd, float scale, int window,
                                             int keep_first, int max_keys, const float* slopes, const float* sinks,
                                             cudaStream_t stream) {
+  return ember_attention_decode_chunked(qkv, kc, vc, out, scratch, positions, seq_slot, pages, max_blocks, T, n_heads, kv_heads,
+                                        hd, vd, scale, window, keep_first, max_keys, slopes, sinks, 0, nullptr, stream);
+}
+
+// The same with sight limited to the query's own chunk (chunk > 0, in place of a window) and one more factor on the
+// scores of every query head (head_scales: float32 per query head, or null).
+EMBER_API int ember_attention_decode_chunked(const void* qkv, const void* kc, const void* vc, void* out, float* scratch,
+                                             const int* positions, const int* seq_slot, const int* pages, int max_blocks,
+                                             int T, int n_heads, int kv_heads, int hd, int vd, float scale, int window,
+                                             int keep_first, int max_keys, const float* slopes, const float* sinks, int chunk,
+                                             const float* head_scales, cudaStream_t stream) {
+  EMBER_CHECK(chunk >= 0 && (chunk == 0 || (window == 0 && keep_first == 0)), "attention_decode_kept: chunk %d beside window %d",
+              chunk, window);
   EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0 && max_keys > 0, "attention_decode_kept: bad sizes");
   EMBER_CHECK(n_heads % kv_heads == 0, "attention_decode_kept: %d heads are not a multiple of %d key/value heads", n_heads,
               kv_heads);
@@ -254,7 +277,7 @@ EMBER_API int ember_attention_decode_biased(const void* qkv, const void* kc, con
   const int per_up = per <= 1 ? 1 : per <= 2 ? 2 : per <= 4 ? 4 : 8;
 #define EMBER_KEPT(PER, DPL)                                                                                              \
   launch_partial<PER, DPL>(grid, stream, qkv, kc, vc, scratch, positions, seq_slot, pages, max_blocks, n_heads, kv_heads, \
-                           hd, vd, scale, window, keep_first, n_chunks, slopes)
+                           hd, vd, scale, window, keep_first, n_chunks, slopes, chunk, head_scales)
 #define EMBER_KEPT_PER(PER)          \
   do {                               \
     if (dpl == 1) EMBER_KEPT(PER, 1); \

@@ -139,8 +139,9 @@ __global__ void __launch_bounds__(128)
 attention_plain_kernel(const T* __restrict__ qkv, const T* __restrict__ kc, const T* __restrict__ vc,
                        T* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ token_seq,
                        const int* __restrict__ seq_slot, const int* __restrict__ pages, int max_blocks, int T_tokens,
-                       int n_heads, int kv_heads, int hd, float scale, int window, int vd, int keep_first,
-                       const float* __restrict__ slopes, const float* __restrict__ sinks) {
+                       int n_heads, int kv_heads, int hd, float scale_all, int window, int vd, int keep_first,
+                       const float* __restrict__ slopes, const float* __restrict__ sinks, int chunk,
+                       const float* __restrict__ head_scales) {
   __shared__ float q_s[4][kMaxHeadDim];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int item = blockIdx.x * 4 + warp;
@@ -155,7 +156,9 @@ attention_plain_kernel(const T* __restrict__ qkv, const T* __restrict__ kc, cons
   }
   const int p = positions[t];
   const int g = h / (n_heads / kv_heads);
-  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  // the first visible key: the window's, or (chunk > 0) the first position of the query's own run of `chunk` positions
+  const int lo = chunk > 0 ? p / chunk * chunk : (window > 0 ? max(0, p - window + 1) : 0);
+  const float scale = head_scales ? scale_all * head_scales[h] : scale_all;    // one more factor a query head
   const int* my_pages = pages + (size_t)s * max_blocks;
   const T* q = qkv + (size_t)t * qkv_width + (size_t)h * hd;
   for (int d = lane; d < hd; d += 32) q_s[warp][d] = to_float(q[d]);
@@ -237,10 +240,29 @@ EMBER_API int ember_attention_plain(const void* qkv, const void* kc, const void*
 // window: query p sees key j <= p if p - j < window or j < keep_first (window 0: all keys).  slopes (float32 per
 // query head, or null): the score of key j loses slopes[h] * (p - j).  sinks (float32 per query head, or null): the
 // softmax's denominator also holds exp(sinks[h]).
+EMBER_API int ember_attention_plain_chunked(const void* qkv, const void* kc, const void* vc, void* out, const int* positions,
+                                            const int* token_seq, const int* seq_slot, const int* pages, int max_blocks, int T,
+                                            int n_heads, int kv_heads, int hd, float scale, int window, int vd, int keep_first,
+                                            const float* slopes, const float* sinks, int chunk, const float* head_scales,
+                                            int dtype, cudaStream_t stream);
+
 EMBER_API int ember_attention_plain_biased(const void* qkv, const void* kc, const void* vc, void* out, const int* positions,
                                            const int* token_seq, const int* seq_slot, const int* pages, int max_blocks, int T,
                                            int n_heads, int kv_heads, int hd, float scale, int window, int vd, int keep_first,
                                            const float* slopes, const float* sinks, int dtype, cudaStream_t stream) {
+  return ember_attention_plain_chunked(qkv, kc, vc, out, positions, token_seq, seq_slot, pages, max_blocks, T, n_heads, kv_heads,
+                                       hd, scale, window, vd, keep_first, slopes, sinks, 0, nullptr, dtype, stream);
+}
+
+// The same with sight limited to the query's own chunk (chunk > 0, in place of a window: query p sees key j <= p
+// with floor(j / chunk) = floor(p / chunk)) and one more factor on the scores of every query head (head_scales:
+// float32 per query head, or null).
+EMBER_API int ember_attention_plain_chunked(const void* qkv, const void* kc, const void* vc, void* out, const int* positions,
+                                            const int* token_seq, const int* seq_slot, const int* pages, int max_blocks, int T,
+                                            int n_heads, int kv_heads, int hd, float scale, int window, int vd, int keep_first,
+                                            const float* slopes, const float* sinks, int chunk, const float* head_scales,
+                                            int dtype, cudaStream_t stream) {
+  EMBER_CHECK(chunk >= 0 && (chunk == 0 || (window == 0 && keep_first == 0)), "attention: chunk %d beside window %d", chunk, window);
   EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0, "attention: bad sizes");
   EMBER_CHECK(n_heads % kv_heads == 0, "attention: %d heads are not a multiple of %d key/value heads", n_heads,
               kv_heads);
@@ -252,11 +274,12 @@ EMBER_API int ember_attention_plain_biased(const void* qkv, const void* kc, cons
   if (dtype == EMBER_F32)
     attention_plain_kernel<float><<<grid, 128, 0, stream>>>((const float*)qkv, (const float*)kc, (const float*)vc,
                                                             (float*)out, positions, token_seq, seq_slot, pages,
-                                                            max_blocks, T, n_heads, kv_heads, hd, scale, window, vd, keep_first, slopes, sinks);
+                                                            max_blocks, T, n_heads, kv_heads, hd, scale, window, vd, keep_first, slopes, sinks, chunk, head_scales);
   else if (dtype == EMBER_BF16)
     attention_plain_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
         (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, positions,
-        token_seq, seq_slot, pages, max_blocks, T, n_heads, kv_heads, hd, scale, window, vd, keep_first, slopes, sinks);
+        token_seq, seq_slot, pages, max_blocks, T, n_heads, kv_heads, hd, scale, window, vd, keep_first, slopes, sinks, chunk,
+        head_scales);
   else
     return ember_fail("attention: element type %d", dtype);
   EMBER_LAUNCH_OK("attention_plain");

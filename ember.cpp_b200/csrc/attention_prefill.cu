@@ -70,8 +70,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloa
                          const __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ out,
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                          const int* __restrict__ seq_new, const int* __restrict__ cu_new,
-                         const int* __restrict__ pages, int max_blocks, int n_heads, int kv_heads, float scale_log2,
-                         int window, int keep_first, const float* __restrict__ slopes, const float* __restrict__ sinks) {
+                         const int* __restrict__ pages, int max_blocks, int n_heads, int kv_heads, float scale_log2_all,
+                         int window, int keep_first, const float* __restrict__ slopes, const float* __restrict__ sinks,
+                         int chunk, const float* __restrict__ head_scales) {
   constexpr int LD = HD + 8, KS = HD / 16;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -95,7 +96,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloa
   }
   const int p0 = seq_start[s] + tile * kRows;  // position of the tile's first row
   const int p_last = p0 + rows - 1;
-  const int kb_first = window > 0 ? max(0, p0 - window + 1) / kRows : 0;
+  // chunk > 0: a query sees the keys of its own run of `chunk` positions alone (in place of a window)
+  const float scale_log2 = head_scales ? scale_log2_all * head_scales[h] : scale_log2_all;   // (a factor above zero)
+  const int kb_first = chunk > 0 ? (p0 / chunk * chunk) / kRows : (window > 0 ? max(0, p0 - window + 1) / kRows : 0);
   const int kb_last = p_last / kRows;
   // pages of kept first positions before the window's first page, and the trips of the page loop
   const int n_kept = window > 0 ? min((keep_first + kRows - 1) / kRows, kb_first) : 0;
@@ -172,7 +175,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloa
           sc[i][j] = fmaf(-slope_raw, (float)(row_pos[j >> 1] - (key0 + i * 8 + c2 + (j & 1))), sc[i][j]);
     }
     // mask by selection where the page crosses a query's position or its window's start
-    const bool need_mask = key0 + kRows - 1 > p0 + warp * 16 || (window > 0 && key0 < p_last - window + 1);  // (kept pages too)
+    const bool need_mask = key0 + kRows - 1 > p0 + warp * 16 || (window > 0 && key0 < p_last - window + 1) ||  // (kept pages too)
+                           (chunk > 0 && key0 < p_last / chunk * chunk);
     if (need_mask) {
 #pragma unroll
       for (int i = 0; i < 8; ++i)
@@ -180,7 +184,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloa
         for (int j = 0; j < 4; ++j) {
           const int key = key0 + i * 8 + c2 + (j & 1);
           const int pos = row_pos[j >> 1];
-          const bool seen = key <= pos && (window <= 0 || key > pos - window || key < keep_first);
+          const bool seen = key <= pos && (window <= 0 || key > pos - window || key < keep_first) &&
+                            (chunk <= 0 || key >= pos / chunk * chunk);
           if (!seen) sc[i][j] = -INFINITY;
         }
     }
@@ -265,7 +270,7 @@ template <int HD>
 int launch(const void* qkv, const void* kc, const void* vc, void* out, const int* seq_slot, const int* seq_start,
            const int* seq_new, const int* cu_new, const int* pages, int max_blocks, int n_seqs, int max_new,
            int n_heads, int kv_heads, float scale, int window, int keep_first, const float* slopes, const float* sinks,
-           cudaStream_t stream) {
+           int chunk, const float* head_scales, cudaStream_t stream) {
   const int smem = 5 * kRows * (HD + 8) * (int)sizeof(__nv_bfloat16);
   static bool configured = false;  // per instantiation
   if (!configured) {
@@ -277,7 +282,7 @@ int launch(const void* qkv, const void* kc, const void* vc, void* out, const int
   attention_prefill_kernel<HD><<<grid, kThreads, smem, stream>>>(
       (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, seq_slot,
       seq_start, seq_new, cu_new, pages, max_blocks, n_heads, kv_heads, scale * 1.4426950408889634f, window, keep_first, slopes,
-      sinks);
+      sinks, chunk, head_scales);
   EMBER_LAUNCH_OK("attention_prefill");
   return 0;
 }
@@ -309,6 +314,12 @@ EMBER_API int ember_attention_prefill(const void* qkv, const void* kc, const voi
                                       max_new, n_heads, kv_heads, hd, scale, window, 0, stream);
 }
 
+EMBER_API int ember_attention_prefill_chunked(const void* qkv, const void* kc, const void* vc, void* out, const int* seq_slot,
+                                              const int* seq_start, const int* seq_new, const int* cu_new, const int* pages,
+                                              int max_blocks, int n_seqs, int max_new, int n_heads, int kv_heads, int hd,
+                                              float scale, int window, int keep_first, const float* slopes, const float* sinks,
+                                              int chunk, const float* head_scales, cudaStream_t stream);
+
 // The same with a distance penalty (slopes: float32 per query head, or null) and a sink in the softmax's denominator
 // (sinks: float32 per query head, or null).
 EMBER_API int ember_attention_prefill_biased(const void* qkv, const void* kc, const void* vc, void* out, const int* seq_slot,
@@ -316,6 +327,20 @@ EMBER_API int ember_attention_prefill_biased(const void* qkv, const void* kc, co
                                              int max_blocks, int n_seqs, int max_new, int n_heads, int kv_heads, int hd,
                                              float scale, int window, int keep_first, const float* slopes, const float* sinks,
                                              cudaStream_t stream) {
+  return ember_attention_prefill_chunked(qkv, kc, vc, out, seq_slot, seq_start, seq_new, cu_new, pages, max_blocks, n_seqs,
+                                         max_new, n_heads, kv_heads, hd, scale, window, keep_first, slopes, sinks, 0, nullptr, stream);
+}
+
+// The same with sight limited to the query's own chunk (chunk > 0, in place of a window: query p sees key j <= p with
+// floor(j / chunk) = floor(p / chunk)) and one more factor, above zero, on the scores of every query head
+// (head_scales: float32 per query head, or null).
+EMBER_API int ember_attention_prefill_chunked(const void* qkv, const void* kc, const void* vc, void* out, const int* seq_slot,
+                                              const int* seq_start, const int* seq_new, const int* cu_new, const int* pages,
+                                              int max_blocks, int n_seqs, int max_new, int n_heads, int kv_heads, int hd,
+                                              float scale, int window, int keep_first, const float* slopes, const float* sinks,
+                                              int chunk, const float* head_scales, cudaStream_t stream) {
+  EMBER_CHECK(chunk >= 0 && (chunk == 0 || (window == 0 && keep_first == 0)), "attention_prefill: chunk %d beside window %d", chunk,
+              window);
   EMBER_CHECK(n_seqs > 0 && max_new > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0, "attention_prefill: bad sizes");
   EMBER_CHECK(n_heads % kv_heads == 0, "attention_prefill: %d heads are not a multiple of %d key/value heads", n_heads,
               kv_heads);
@@ -328,7 +353,7 @@ EMBER_API int ember_attention_prefill_biased(const void* qkv, const void* kc, co
 #define EMBER_PREFILL(HD)                                                                                           \
   case HD:                                                                                                          \
     return launch<HD>(qkv, kc, vc, out, seq_slot, seq_start, seq_new, cu_new, pages, max_blocks, n_seqs, max_new,   \
-                      n_heads, kv_heads, scale, window, keep_first, slopes, sinks, stream)
+                      n_heads, kv_heads, scale, window, keep_first, slopes, sinks, chunk, head_scales, stream)
   switch (hd) {
     EMBER_PREFILL(16);
     EMBER_PREFILL(32);

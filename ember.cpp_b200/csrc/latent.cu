@@ -43,16 +43,17 @@ __device__ __forceinline__ void turn(float u, float v, int position, float f, fl
 template <typename TS, typename TD>
 __global__ void rotate_kernel(const TS* src, long long src_stride, int src_col, int src_head, TD* dst, long long dst_stride,
                               int dst_col, int dst_head, int width, const int* __restrict__ positions,
-                              const float* __restrict__ freqs, float magnitude, int dims) {
+                              const float* __restrict__ freqs, float magnitude, int dims, int interleaved) {
   const int t = blockIdx.x, h = blockIdx.y, half = dims / 2;
   const TS* s = src + (size_t)t * src_stride + src_col + (size_t)h * src_head;
   TD* d = dst + (size_t)t * dst_stride + dst_col + (size_t)h * dst_head;
   const int p = positions[t];
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     float ou, ov;
-    turn(to_float(s[i]), to_float(s[i + half]), p, freqs[i], magnitude, ou, ov);
-    d[i] = from_float<TD>(ou);
-    d[i + half] = from_float<TD>(ov);
+    const int iu = interleaved ? 2 * i : i, iv = interleaved ? 2 * i + 1 : i + half;   // pair i: neighbours, or half apart
+    turn(to_float(s[iu]), to_float(s[iv]), p, freqs[i], magnitude, ou, ov);
+    d[iu] = from_float<TD>(ou);
+    d[iv] = from_float<TD>(ov);
   }
   for (int i = dims + threadIdx.x; i < width; i += blockDim.x) d[i] = from_float<TD>(to_float(s[i]));
 }
@@ -213,16 +214,30 @@ latent_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ kc,
 }  // namespace
 
 // src [T, *] of element type src_dtype, dst [T, *] of dst_dtype (row strides in elements); see rotate_kernel.
+EMBER_API int ember_rotate_pairs(const void* src, long long src_stride, int src_col, int src_head, int src_dtype, void* dst,
+                                 long long dst_stride, int dst_col, int dst_head, int dst_dtype, int T, int heads, int width,
+                                 const int* positions, const float* freqs, float magnitude, int dims, int interleaved,
+                                 cudaStream_t stream);
+
 EMBER_API int ember_rotate(const void* src, long long src_stride, int src_col, int src_head, int src_dtype, void* dst,
                            long long dst_stride, int dst_col, int dst_head, int dst_dtype, int T, int heads, int width,
                            const int* positions, const float* freqs, float magnitude, int dims, cudaStream_t stream) {
+  return ember_rotate_pairs(src, src_stride, src_col, src_head, src_dtype, dst, dst_stride, dst_col, dst_head, dst_dtype, T, heads,
+                            width, positions, freqs, magnitude, dims, 0, stream);
+}
+
+// The same with the pairing as an argument: interleaved 0 pairs dimension i with i + dims / 2, 1 pairs 2i with 2i + 1.
+EMBER_API int ember_rotate_pairs(const void* src, long long src_stride, int src_col, int src_head, int src_dtype, void* dst,
+                                 long long dst_stride, int dst_col, int dst_head, int dst_dtype, int T, int heads, int width,
+                                 const int* positions, const float* freqs, float magnitude, int dims, int interleaved,
+                                 cudaStream_t stream) {
   EMBER_CHECK(T > 0 && heads > 0 && heads <= 65535 && width > 0, "rotate: bad sizes");
   EMBER_CHECK(dims > 0 && dims % 2 == 0 && dims <= width, "rotate: %d rotated dimensions of %d", dims, width);
   const dim3 grid(T, heads);
   const int threads = dims / 2 >= 64 || width - dims >= 64 ? 128 : 32;
 #define EMBER_ROTATE(TS, TD)                                                                                          \
   rotate_kernel<TS, TD><<<grid, threads, 0, stream>>>((const TS*)src, src_stride, src_col, src_head, (TD*)dst, dst_stride, \
-                                                      dst_col, dst_head, width, positions, freqs, magnitude, dims)
+                                                      dst_col, dst_head, width, positions, freqs, magnitude, dims, interleaved)
   if (src_dtype == EMBER_F32 && dst_dtype == EMBER_F32)
     EMBER_ROTATE(float, float);
   else if (src_dtype == EMBER_BF16 && dst_dtype == EMBER_BF16)

@@ -25,7 +25,7 @@ moe_route_kernel(const int* __restrict__ tokens, const int* __restrict__ table, 
   for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
   __syncthreads();
   for (int q = threadIdx.x; q < n_pairs; q += blockDim.x) {
-    int tok = tokens[q / top];
+    int tok = tokens ? tokens[q / top] : q / top;     // (no ids: the table's row t is token t's choice)
     tok = min(max(tok, 0), vocab - 1);
     int e = table[(size_t)tok * top + q % top];
     e = min(max(e, 0), experts - 1);
@@ -68,6 +68,16 @@ __device__ __forceinline__ float warp_dot(const T* __restrict__ w, const T* a, i
   return warp_sum(acc);
 }
 
+// silu(g) * u, or with limit > 0 the clamped form: g capped at limit, u within +-limit, g * sigmoid(alpha g) * (u + shift)
+__device__ __forceinline__ float gate_value(float g, float u, float limit, float alpha, float shift) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-alpha * g)) * (u + shift);
+  }
+  return g / (1.0f + expf(-g)) * u;
+}
+
 constexpr int kStreamWarps = 8;
 constexpr int kStreamOutputs = 4;  // per warp
 
@@ -75,7 +85,7 @@ constexpr int kStreamOutputs = 4;  // per warp
 template <typename T>
 __global__ void __launch_bounds__(kStreamWarps * 32)
 moe_gate_up_stream_kernel(const T* __restrict__ a, const T* __restrict__ w, const int* __restrict__ pair_expert,
-                          T* __restrict__ out, int top, int width, int inner) {
+                          T* __restrict__ out, int top, int width, int inner, float limit, float alpha, float shift) {
   const int q = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* row = a + (size_t)(q / top) * width;
   const T* we = w + (size_t)pair_expert[q] * 2 * inner * width;
@@ -84,7 +94,7 @@ moe_gate_up_stream_kernel(const T* __restrict__ a, const T* __restrict__ w, cons
     if (f >= inner) return;
     const float g = warp_dot(we + (size_t)f * width, row, width, lane);
     const float u = warp_dot(we + (size_t)(inner + f) * width, row, width, lane);
-    if (lane == 0) out[(size_t)q * inner + f] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    if (lane == 0) out[(size_t)q * inner + f] = from_float<T>(gate_value(g, u, limit, alpha, shift));
   }
 }
 
@@ -141,7 +151,8 @@ constexpr int tile_smem() {
 template <bool GATED>
 __global__ void __launch_bounds__(128)
 moe_tile_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, const int* __restrict__ offsets,
-                const int* __restrict__ sorted, void* __restrict__ out, int experts, int top, int K, int n_out) {
+                const int* __restrict__ sorted, void* __restrict__ out, int experts, int top, int K, int n_out, float limit,
+                float alpha, float shift) {
   constexpr int NW = GATED ? 2 : 1;
   extern __shared__ __align__(16) unsigned char tile_raw[];
   __nv_bfloat16* sA = reinterpret_cast<__nv_bfloat16*>(tile_raw);  // [2][kTileM * kLd]
@@ -257,7 +268,7 @@ moe_tile_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __rest
         if (n >= n_out) continue;
         if constexpr (GATED) {
           const float g0 = acc[0][f][i][2 * r], g1 = acc[0][f][i][2 * r + 1];
-          const float y0 = g0 / (1.0f + expf(-g0)) * acc[1][f][i][2 * r], y1 = g1 / (1.0f + expf(-g1)) * acc[1][f][i][2 * r + 1];
+          const float y0 = gate_value(g0, acc[1][f][i][2 * r], limit, alpha, shift), y1 = gate_value(g1, acc[1][f][i][2 * r + 1], limit, alpha, shift);
           __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(out) + (size_t)q * n_out + n;
           if (n + 1 < n_out)
             *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(y0, y1);
@@ -277,7 +288,8 @@ moe_tile_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __rest
 
 template <bool GATED>
 int launch_tiles(const void* a, const void* w, const int* offsets, const int* sorted, void* out, long long pairs, int experts,
-                 int top, int K, int n_out, cudaStream_t stream, const char* name) {
+                 int top, int K, int n_out, cudaStream_t stream, const char* name, float limit = 0.f, float alpha = 1.f,
+                 float shift = 0.f) {
   static bool configured = false;  // per instantiation
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(moe_tile_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, tile_smem<GATED>());
@@ -287,17 +299,153 @@ int launch_tiles(const void* a, const void* w, const int* offsets, const int* so
   const dim3 grid((unsigned)((pairs + kTileM - 1) / kTileM + experts), (n_out + kTileN - 1) / kTileN);
   EMBER_CHECK(grid.y <= 65535, "%s: %d outputs exceed one launch", name, n_out);
   moe_tile_kernel<GATED><<<grid, 128, tile_smem<GATED>(), stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, offsets,
-                                                                    sorted, out, experts, top, K, n_out);
+                                                                    sorted, out, experts, top, K, n_out, limit, alpha, shift);
   EMBER_LAUNCH_OK(name);
   return 0;
 }
 
+// ---------------------------------------------------------------------------- the router's choice
+// A warp a token.  s = sigmoid(z); the choice is made on s + correction among the experts of the `keep` groups
+// whose two largest choice scores add up to the most; weights = s of the chosen, over their sum (+ 1e-20), times
+// `scale`.  Among equal scores the lower index wins.  Dynamic shared memory: per warp 2 * experts + groups floats.
+constexpr int kPickWarps = 4;
+
+__device__ __forceinline__ void warp_argmax(float& best, int& at) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+    const int oi = __shfl_xor_sync(0xffffffffu, at, off);
+    if (ov > best || (ov == best && oi < at)) {
+      best = ov;
+      at = oi;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(32 * kPickWarps)
+moe_pick_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ correction, int T, int experts, int top,
+                int groups, int keep, float scale, int* __restrict__ chosen, float* __restrict__ weights) {
+  extern __shared__ float pick_sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kPickWarps + warp;
+  if (t >= T) return;
+  float* sc = pick_sm + (size_t)warp * (2 * experts + groups);
+  float* ch = sc + experts;
+  float* gs = ch + experts;
+  for (int e = lane; e < experts; e += 32) {
+    const float s = 1.0f / (1.0f + expf(-logits[(size_t)t * ld + e]));
+    sc[e] = s;
+    ch[e] = s + correction[e];
+  }
+  __syncwarp();
+  if (groups > 1) {
+    const int per = experts / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float m1 = -INFINITY, m2 = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) {
+        const float v = ch[e];
+        if (v > m1) {
+          m2 = m1;
+          m1 = v;
+        } else if (v > m2) {
+          m2 = v;
+        }
+      }
+      gs[g] = per >= 2 ? m1 + m2 : m1;
+    }
+    __syncwarp();
+    for (int it = 0; it < keep; ++it) {     // a kept group's score becomes +inf, which is never picked again
+      float best = -INFINITY;
+      int at = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = gs[g];
+        if (v != INFINITY && (v > best || (v == best && g < at))) {
+          best = v;
+          at = g;
+        }
+      }
+      warp_argmax(best, at);
+      if (lane == 0 && at < groups) gs[at] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+      if (gs[e / per] != INFINITY) ch[e] = -INFINITY;
+    __syncwarp();
+  }
+  float sum = 0.f;      // (every lane keeps the same sum)
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = ch[e];
+      if (v > best || (v == best && e < at)) {
+        best = v;
+        at = e;
+      }
+    }
+    warp_argmax(best, at);
+    if (at >= experts) at = 0;
+    sum += sc[at];
+    if (lane == 0) {
+      chosen[(size_t)t * top + k] = at;
+      weights[(size_t)t * top + k] = sc[at];
+      ch[at] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  const float f = scale / (sum + 1e-20f);
+  for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] *= f;
+}
+
+// grid (T): out = x + sum_k weights[t, k] y[t, k, :] (k ascending) + sigmoid(gate) * shared[t, :]
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ weights,
+                   const float* __restrict__ shared, const float* __restrict__ logits, int ld, int gate_col,
+                   float* __restrict__ out, int top, int width) {
+  const int t = blockIdx.x;
+  const float* w = weights + (size_t)t * top;
+  const float sg = shared == nullptr ? 0.f : (logits == nullptr ? 1.f : 1.0f / (1.0f + expf(-logits[(size_t)t * ld + gate_col])));
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) acc = fmaf(w[k], y[((size_t)t * top + k) * width + c], acc);
+    if (shared != nullptr) acc = fmaf(sg, shared[(size_t)t * width + c], acc);
+    out[(size_t)t * width + c] = x[(size_t)t * width + c] + acc;
+  }
+}
+
 }  // namespace
 
-// tokens [T] (ids), table [vocab, top]; pair_expert [T * top], offsets [experts + 1], sorted [T * top]
+// logits float32 [T, ld] (the first `experts` columns are the router's), correction float32 [experts];
+// chosen int32 [T, top], weights float32 [T, top].
+EMBER_API int ember_moe_pick(const float* logits, int ld, const float* correction, int T, int experts, int top, int groups,
+                             int keep, float scale, int* chosen, float* weights, cudaStream_t stream) {
+  EMBER_CHECK(T > 0 && experts > 0 && experts <= 1024 && top >= 1 && top <= experts && ld >= experts,
+              "moe_pick: %d tokens, top %d of %d experts (at most 1024)", T, top, experts);
+  EMBER_CHECK(groups >= 1 && experts % groups == 0 && keep >= 1 && keep <= groups && (long long)keep * (experts / groups) >= top,
+              "moe_pick: %d groups of which %d are kept do not hold %d choices", groups, keep, top);
+  const size_t smem = (size_t)kPickWarps * (2 * experts + groups) * sizeof(float);
+  const cudaError_t e = launch_plain(moe_pick_kernel, dim3((T + kPickWarps - 1) / kPickWarps), dim3(32 * kPickWarps), smem, stream,
+                                     logits, ld, correction, T, experts, top, groups, keep, scale, chosen, weights);
+  if (e != cudaSuccess) return ember_fail("moe_pick: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+// x, out float32 [T, width]; y float32 [T, top, width]; weights float32 [T, top]; shared float32 [T, width] or null;
+// logits float32 [T, ld] or null (then the shared rows are added as they are): the shared rows' gate is column gate_col.
+EMBER_API int ember_moe_combine(const float* x, const float* y, const float* weights, const float* shared, const float* logits,
+                                int ld, int gate_col, float* out, int T, int top, int width, cudaStream_t stream) {
+  EMBER_CHECK(T > 0 && top > 0 && width > 0, "moe_combine: bad sizes");
+  EMBER_CHECK(logits == nullptr || (gate_col >= 0 && gate_col < ld), "moe_combine: gate column %d of %d", gate_col, ld);
+  const cudaError_t e = launch_plain(moe_combine_kernel, dim3(T), dim3(256), 0, stream, x, y, weights, shared, logits, ld, gate_col,
+                                     out, top, width);
+  if (e != cudaSuccess) return ember_fail("moe_combine: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+// tokens [T] (ids; null: the table's row t is token t's choice), table [vocab, top]; pair_expert [T * top], offsets [experts + 1], sorted [T * top]
 EMBER_API int ember_moe_route(const int* tokens, const int* table, int T, int top, int experts, int vocab, int* pair_expert,
                               int* offsets, int* sorted, cudaStream_t stream) {
-  EMBER_CHECK(T > 0 && top > 0 && experts > 0 && vocab > 0 && top <= experts, "moe_route: bad sizes");
+  EMBER_CHECK(T > 0 && top > 0 && experts > 0 && vocab > 0 && top <= experts && (tokens != nullptr || vocab >= T), "moe_route: bad sizes");
   EMBER_CHECK(experts <= 4096, "moe_route: %d experts (at most 4096)", experts);
   EMBER_CHECK((long long)T * top < (1ll << 30), "moe_route: %d tokens x %d choices", T, top);
   const cudaError_t e = launch_plain(moe_route_kernel, dim3(1), dim3(1024), 2 * experts * sizeof(int), stream, tokens, table,
@@ -308,25 +456,38 @@ EMBER_API int ember_moe_route(const int* tokens, const int* table, int T, int to
 
 // a [T, width] (dtype), w [experts, 2 * inner, width], out [T * top, inner] (dtype).  tiled != 0 (bfloat16 only):
 // the tensor-core tiles; else the streaming form.
+EMBER_API int ember_moe_gate_up_act(const void* a, const void* w, const int* pair_expert, const int* offsets, const int* sorted,
+                                    void* out, int T, int top, int experts, int width, int inner, int tiled, int dtype,
+                                    float limit, float alpha, float shift, cudaStream_t stream);
+
 EMBER_API int ember_moe_gate_up(const void* a, const void* w, const int* pair_expert, const int* offsets, const int* sorted,
                                 void* out, int T, int top, int experts, int width, int inner, int tiled, int dtype,
                                 cudaStream_t stream) {
-  EMBER_CHECK(T > 0 && top > 0 && experts > 0 && width > 0 && inner > 0, "moe_gate_up: bad sizes");
+  return ember_moe_gate_up_act(a, w, pair_expert, offsets, sorted, out, T, top, experts, width, inner, tiled, dtype, 0.f, 1.f, 0.f,
+                               stream);
+}
+
+// The same with the gate's form as arguments: limit 0: silu(g) * u; limit > 0: g capped at limit, u within +-limit,
+// g * sigmoid(alpha g) * (u + shift).
+EMBER_API int ember_moe_gate_up_act(const void* a, const void* w, const int* pair_expert, const int* offsets, const int* sorted,
+                                    void* out, int T, int top, int experts, int width, int inner, int tiled, int dtype,
+                                    float limit, float alpha, float shift, cudaStream_t stream) {
+  EMBER_CHECK(T > 0 && top > 0 && experts > 0 && width > 0 && inner > 0 && limit >= 0.f, "moe_gate_up: bad sizes");
   const long long pairs = (long long)T * top;
   if (tiled) {
     EMBER_CHECK(dtype == EMBER_BF16 && width % 8 == 0 && inner % 2 == 0,
                 "moe_gate_up: tiles take bfloat16 rows that are multiples of 8 and an even number of outputs");
-    return launch_tiles<true>(a, w, offsets, sorted, out, pairs, experts, top, width, inner, stream, "moe_gate_up");
+    return launch_tiles<true>(a, w, offsets, sorted, out, pairs, experts, top, width, inner, stream, "moe_gate_up", limit, alpha, shift);
   }
   const dim3 grid((unsigned)pairs, (inner + kStreamWarps * kStreamOutputs - 1) / (kStreamWarps * kStreamOutputs));
   EMBER_CHECK(grid.y <= 65535, "moe_gate_up: %d outputs exceed one launch", inner);
   cudaError_t e;
   if (dtype == EMBER_F32)
     e = launch_plain(moe_gate_up_stream_kernel<float>, grid, dim3(kStreamWarps * 32), 0, stream, (const float*)a, (const float*)w,
-                   pair_expert, (float*)out, top, width, inner);
+                   pair_expert, (float*)out, top, width, inner, limit, alpha, shift);
   else if (dtype == EMBER_BF16)
     e = launch_plain(moe_gate_up_stream_kernel<__nv_bfloat16>, grid, dim3(kStreamWarps * 32), 0, stream, (const __nv_bfloat16*)a,
-                   (const __nv_bfloat16*)w, pair_expert, (__nv_bfloat16*)out, top, width, inner);
+                   (const __nv_bfloat16*)w, pair_expert, (__nv_bfloat16*)out, top, width, inner, limit, alpha, shift);
   else
     return ember_fail("moe_gate_up: element type %d", dtype);
   if (e != cudaSuccess) return ember_fail("moe_gate_up: %s", cudaGetErrorString(e));

@@ -24,6 +24,32 @@ _LT_WORKSPACE = 32 << 20
 _c_int, _c_float, _c_void, _c_size, _c_u64 = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint64
 
 _SIGNATURES = {
+    "ember_token_shift": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
+    "ember_side_input": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void,
+                         _c_void, _c_float, _c_int, _c_int, _c_int, _c_void],
+    "ember_low_rank_out": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int,
+                           _c_void],
+    "ember_gla_scan": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_void, _c_float, _c_void, _c_void, _c_void, _c_void,
+                       _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ember_generalized_delta_rule": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_float,
+                                     _c_float, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ember_moe_pick": [_c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void, _c_void, _c_void],
+    "ember_moe_combine": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_int, _c_int, _c_void],
+    "ember_moe_gate_up_act": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
+                              _c_int, _c_int, _c_float, _c_float, _c_float, _c_void],
+    "ember_conv_act": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void,
+                       _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ember_rotate_pairs": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_void, ctypes.c_longlong, _c_int, _c_int, _c_int,
+                           _c_int, _c_int, _c_int, _c_void, _c_void, _c_float, _c_int, _c_int, _c_void],
+    "ember_attention_plain_chunked": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
+                                      _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void,
+                                      _c_int, _c_void],
+    "ember_attention_prefill_chunked": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
+                                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void, _c_void,
+                                        _c_int, _c_void, _c_void],
+    "ember_attention_decode_chunked": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
+                                       _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int,
+                                       _c_void, _c_void],
     "ember_embed": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_int, _c_float,
                     _c_void],
     "ember_layernorm": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_void],
@@ -614,7 +640,8 @@ class CudaOps:
                    _code(qkv.dtype))
 
     def attention(self, qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype, store=False,
-                  keep_first=None, value_dim=None, slopes=None, sinks=None):
+                  keep_first=None, value_dim=None, slopes=None, sinks=None, chunk=0, head_scales=None,
+                  head_scales_positive=True):
         """Causal attention of the step's tokens over the cache.  With `store` their own keys and
         values are written into the cache first (in the same launch where a kernel can).
         float32: the plain kernel, whose sums depend on positions alone.  bfloat16: one token per
@@ -625,16 +652,23 @@ class CudaOps:
         every head size, or for prompts in bfloat16 the mma.sync kernel where it has the head size.
         slopes (float32 per query head): the score of a key loses slopes[h] times its distance to the query.
         sinks (float32 per query head): the softmax's denominator also holds exp(sinks[h]), a term without a
-        key or a value.  Both go the way of keep_first / value_dim."""
+        key or a value.  Both go the way of keep_first / value_dim.
+        chunk > 0 (in place of a window): a query at position p sees key j <= p only if floor(j / chunk) =
+        floor(p / chunk).  head_scales (float32 per query head): one more factor on a head's scores; the
+        tensor-core prompt kernel takes it where every factor is above zero (`head_scales_positive`).  Both go
+        the same way too."""
         if qkv.dtype != cache.k.dtype or out_dtype != qkv.dtype:
             raise KernelError("attention: activations, cache and output have one element type")
         self._dense(qkv, "qkv")
-        for name, t in (("slopes", slopes), ("sinks", sinks)):
+        for name, t in (("slopes", slopes), ("sinks", sinks), ("head_scales", head_scales)):
             if t is not None and (t.dtype != torch.float32 or tuple(t.shape) != (n_heads,) or not t.is_cuda):
                 raise KernelError(f"attention: {name} are float32 values, one a query head")
-        if keep_first is not None or value_dim is not None or slopes is not None or sinks is not None:
+        if chunk < 0 or (chunk and (window or keep_first)):
+            raise KernelError(f"attention: chunk {chunk} beside window {window} and {keep_first} kept positions")
+        if keep_first is not None or value_dim is not None or slopes is not None or sinks is not None or chunk or head_scales is not None:
             return self._attention_kept(qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype, store,
-                                        int(keep_first or 0), head_dim if value_dim is None else int(value_dim), slopes, sinks)
+                                        int(keep_first or 0), head_dim if value_dim is None else int(value_dim), slopes, sinks,
+                                        int(chunk), head_scales, head_scales_positive)
         out = torch.empty((plan.T, n_heads * head_dim), dtype=out_dtype, device=qkv.device)
         pages = plan.pages[cache.group_index]
         if qkv.dtype == torch.bfloat16 and plan.all_single:
@@ -689,7 +723,7 @@ class CudaOps:
         return out
 
     def _attention_kept(self, qkv, cache, plan, n_heads, kv_heads, hd, scale, window, out_dtype, store, keep_first, vd,
-                        slopes=None, sinks=None):
+                        slopes=None, sinks=None, chunk=0, head_scales=None, head_scales_positive=True):
         if qkv.shape[1] != (n_heads + kv_heads) * hd + kv_heads * vd:
             raise KernelError(f"attention: rows of {qkv.shape[1]} values are not q | k | v of {n_heads} x {hd}, "
                               f"{kv_heads} x {hd} and {kv_heads} x {vd}")
@@ -704,28 +738,29 @@ class CudaOps:
         fast = self.attention_kept_fast and qkv.dtype == torch.bfloat16
         if fast and plan.all_single and plan.T == plan.n:
             # one token each: the visible keys in chunks of 128, a block a chunk and key/value head, then the merge
-            max_keys = min(keep_first + window, plan.max_end) if window > 0 else plan.max_end
+            max_keys = min(keep_first + window, plan.max_end) if window > 0 else (min(chunk, plan.max_end) if chunk else plan.max_end)
             scratch = torch.empty(self.lib.ember_attention_decode_kept_scratch(plan.T, n_heads, vd, max_keys),
                                   dtype=torch.float32, device=qkv.device)
-            rc = self._call("ember_attention_decode_biased", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+            rc = self._call("ember_attention_decode_chunked", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
                             out.data_ptr(), scratch.data_ptr(), plan.positions.data_ptr(), plan.seq_slot.data_ptr(),
                             pages.data_ptr(), plan.max_blocks, plan.T, n_heads, kv_heads, hd, vd, float(scale), int(window),
-                            keep_first, int(max_keys), self._ptr(slopes), self._ptr(sinks), allow=(2,))
+                            keep_first, int(max_keys), self._ptr(slopes), self._ptr(sinks), chunk, self._ptr(head_scales),
+                            allow=(2,))
             if rc == 0:
                 self.launches += 1      # (the merge)
                 return out
-        if fast and vd == hd and hd % 16 == 0 and hd <= 128 and scale > 0 and not plan.all_single:
-            rc = self._call("ember_attention_prefill_biased", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+        if fast and vd == hd and hd % 16 == 0 and hd <= 128 and scale > 0 and not plan.all_single and head_scales_positive:
+            rc = self._call("ember_attention_prefill_chunked", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
                             out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.seq_new.data_ptr(),
                             plan.cu_new.data_ptr(), pages.data_ptr(), plan.max_blocks, plan.n, plan.max_new, n_heads,
-                            kv_heads, hd, float(scale), int(window), keep_first, self._ptr(slopes), self._ptr(sinks),
-                            allow=(2,))
+                            kv_heads, hd, float(scale), int(window), keep_first, self._ptr(slopes), self._ptr(sinks), chunk,
+                            self._ptr(head_scales), allow=(2,))
             if rc == 0:
                 return out
-        self._call("ember_attention_plain_biased", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), out.data_ptr(),
+        self._call("ember_attention_plain_chunked", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), out.data_ptr(),
                    plan.positions.data_ptr(), plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), pages.data_ptr(),
                    plan.max_blocks, plan.T, n_heads, kv_heads, hd, float(scale), int(window), vd, keep_first,
-                   self._ptr(slopes), self._ptr(sinks), _code(qkv.dtype))
+                   self._ptr(slopes), self._ptr(sinks), chunk, self._ptr(head_scales), _code(qkv.dtype))
         return out
 
     # ------------------------------------------------------------------ branches side by side
@@ -801,8 +836,8 @@ class CudaOps:
         return out
 
     # ------------------------------------------------------------------ Mamba-2
-    def conv_silu(self, proj, col0, channels, conv_w, conv_b, conv_state, plan):
-        """silu of the causal convolution (conv_w [channels, taps], the last tap on the current token) of
+    def conv_silu(self, proj, col0, channels, conv_w, conv_b, conv_state, plan, act="silu"):
+        """silu (act "none": nothing) of the causal convolution (conv_w [channels, taps], the last tap on the current token) of
         `channels` columns from col0 of `proj`, per sequence of the step; conv_state [slots, taps - 1, channels]
         float32 carries the rows before the step and is advanced."""
         taps = conv_w.shape[1]
@@ -812,10 +847,12 @@ class CudaOps:
             raise KernelError("conv_silu: the state is float32 [slots, taps - 1, channels]")
         self._dense(proj, "conv input")
         out = torch.empty((plan.T, channels), dtype=proj.dtype, device=proj.device)
-        self._call("ember_conv_silu", proj.data_ptr(), proj.stride(0), int(col0), int(channels), int(taps), conv_w.data_ptr(),
+        if act not in ("silu", "none"):
+            raise KernelError(f"conv_silu: activation {act!r}")
+        self._call("ember_conv_act", proj.data_ptr(), proj.stride(0), int(col0), int(channels), int(taps), conv_w.data_ptr(),
                    conv_b.data_ptr(), self._ptr(conv_state), out.data_ptr(), plan.token_seq.data_ptr(),
                    plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.cu_new.data_ptr(), plan.T, plan.n,
-                   max(int(plan.max_new), 1), 1 if plan.all_single else 0, _code(proj.dtype))
+                   max(int(plan.max_new), 1), 1 if plan.all_single else 0, _code(proj.dtype), 0 if act == "silu" else 1)
         return out
 
     SSD_PIECES_FROM = 128   # new tokens of a step's longest sequence from which the recurrence runs as matrix products
@@ -1036,18 +1073,20 @@ class CudaOps:
         return x
 
     # ------------------------------------------------------------------ rotation, rows of low rank, products per head
-    def rotate(self, src, dst, positions, heads, src_col, src_head, dst_col, dst_head, width, freqs, magnitude, dims):
+    def rotate(self, src, dst, positions, heads, src_col, src_head, dst_col, dst_head, width, freqs, magnitude, dims,
+               interleaved=False):
         """For every token t and head h < heads: `width` values from column src_col + h * src_head of src, their first
         `dims` rotated by the token's position (pair i with i + dims / 2, angle position * freqs[i], cos and sin times
-        `magnitude`), written to column dst_col + h * dst_head of dst.  src and dst may be one tensor."""
+        `magnitude`), written to column dst_col + h * dst_head of dst.  src and dst may be one tensor.  `interleaved`:
+        pair i is dimensions 2i and 2i + 1."""
         T = src.shape[0]
         if src.stride(1) != 1 or dst.stride(1) != 1 or dst.shape[0] != T or freqs.dtype != torch.float32 or freqs.numel() != dims // 2:
             raise KernelError("rotate: rows of contiguous values, a float32 frequency for every pair")
         if src_col + (heads - 1) * src_head + width > src.shape[1] or dst_col + (heads - 1) * dst_head + width > dst.shape[1]:
             raise KernelError("rotate: the heads do not fit the rows")
-        self._call("ember_rotate", src.data_ptr(), src.stride(0), int(src_col), int(src_head), _code(src.dtype), dst.data_ptr(),
+        self._call("ember_rotate_pairs", src.data_ptr(), src.stride(0), int(src_col), int(src_head), _code(src.dtype), dst.data_ptr(),
                    dst.stride(0), int(dst_col), int(dst_head), _code(dst.dtype), T, int(heads), int(width),
-                   positions.data_ptr(), freqs.data_ptr(), float(magnitude), int(dims))
+                   positions.data_ptr(), freqs.data_ptr(), float(magnitude), int(dims), 1 if interleaved else 0)
         return dst
 
     def latent_rows(self, down, plan, q_rank, q_norm, kv_norm, kv_rank, rot_dim, eps, rotary, cache, out_dtype):
@@ -1157,13 +1196,81 @@ class CudaOps:
         self.launches += 2 if chunked else 1      # (the prepare kernel, the chunks' factors)
         return out
 
+    # ------------------------------------------------------------------ token shift, per-layer token input
+    def token_shift(self, h, mu, state, plan):
+        """h[t] + (h[t-1] - h[t]) * mu per sequence of the step, the row before a sequence's first token of the step being
+        state[slot] (zeros at position 0); state [slots, width] float32 then holds each sequence's last row."""
+        T, width = h.shape
+        if mu.dtype != torch.float32 or mu.numel() != width or state.dtype != torch.float32 or state.shape[1] != width:
+            raise KernelError("token_shift: a float32 blend vector and float32 state rows of the rows' width")
+        out = torch.empty_like(h)
+        self._call("ember_token_shift", self._dense(h, "rows").data_ptr(), out.data_ptr(), mu.data_ptr(), state.data_ptr(),
+                   plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.cu_new.data_ptr(), T, width,
+                   _code(h.dtype))
+        return out
+
+    def side_input(self, x, plan, table, col, dim, w_gate, w_proj, w_norm, eps):
+        """x + unit_rms(W_proj (gelu_tanh(W_gate x) * e)) * w_norm, e = `dim` columns from `col` of each token's row of
+        `table`; float32 rows in, a new float32 tensor out."""
+        T, width = x.shape
+        if x.dtype != torch.float32 or table.dtype != w_gate.dtype or w_proj.dtype != w_gate.dtype or \
+                tuple(w_gate.shape) != (dim, width) or tuple(w_proj.shape) != (width, dim) or w_norm.numel() != width:
+            raise KernelError("side_input: a float32 stream, the table and both matrices of one element type and fitting sizes")
+        out = torch.empty_like(x)
+        self._call("ember_side_input", self._dense(x, "stream").data_ptr(), out.data_ptr(), plan.tokens.data_ptr(),
+                   plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), table.data_ptr(), table.shape[0], table.shape[1], int(col),
+                   int(dim), w_gate.data_ptr(), w_proj.data_ptr(), w_norm.data_ptr(), float(eps), T, width, _code(w_gate.dtype))
+        return out
+
+    # ------------------------------------------------------------------ linear attention, the generalized delta rule
+    def low_rank_out(self, proj, col, w2, bias, act):
+        """bias + act(proj[:, col : col + rank]) W2^T with float32 sums: the second half of a product of low rank;
+        w2 float32 [n_out, rank], act "none" or "tanh".  float32 [T, n_out]."""
+        n_out, rank = w2.shape
+        if act not in ("none", "tanh") or w2.dtype != torch.float32 or bias.dtype != torch.float32 or bias.numel() != n_out \
+                or col + rank > proj.shape[1] or proj.stride(1) != 1:
+            raise KernelError("low_rank_out: float32 [outputs, rank] and bias, the rank's columns inside the rows")
+        out = torch.empty((proj.shape[0], n_out), dtype=torch.float32, device=proj.device)
+        self._call("ember_low_rank_out", proj.data_ptr(), proj.stride(0), int(col), rank, w2.data_ptr(), bias.data_ptr(),
+                   out.data_ptr(), proj.shape[0], n_out, 1 if act == "tanh" else 0, _code(proj.dtype))
+        return out
+
+    def gla_scan(self, proj, q_col, k_col, v_col, z, tau, state, plan, heads, dim, vdim):
+        """Gated linear attention token by token: S <- diag(sigmoid(z)^(1/tau)) S + k v^T, o = S^T (q dim^(-1/2)); q, k, v
+        from columns of `proj`, z float32 [T, heads * dim], state float32 [slots, heads, dim, vdim].  float32 [T, heads * vdim]."""
+        T = proj.shape[0]
+        if z.dtype != torch.float32 or tuple(z.shape) != (T, heads * dim) or state.dtype != torch.float32 or \
+                tuple(state.shape[1:]) != (heads, dim, vdim) or proj.stride(1) != 1:
+            raise KernelError("gla_scan: float32 decays [T, heads * dim] and state [slots, heads, dim, vdim]")
+        out = torch.empty((T, heads * vdim), dtype=torch.float32, device=proj.device)
+        self._call("ember_gla_scan", proj.data_ptr(), proj.stride(0), int(q_col), int(k_col), int(v_col), self._dense(z, "z").data_ptr(),
+                   float(tau), state.data_ptr(), out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(),
+                   plan.cu_new.data_ptr(), plan.n, heads, dim, vdim, _code(proj.dtype))
+        return out
+
+    def generalized_delta_rule(self, proj, r_col, k_col, v_col, a_col, a_bias, wz, decay_coef, state, plan, heads, dim, unit_eps):
+        """S <- diag(w) S - (a u)(u^T S) + k v^T, o = S^T r, with w = exp(-decay_coef * sigmoid(wz)), a = sigmoid(a_in +
+        a_bias), u the unit key; r, k, v, a_in from columns of `proj`, wz float32 [T, heads * dim], state float32
+        [slots, heads, dim, dim].  float32 [T, heads * dim]."""
+        T, m = proj.shape[0], heads * dim
+        if wz.dtype != torch.float32 or tuple(wz.shape) != (T, m) or state.dtype != torch.float32 or a_bias.numel() != m or \
+                tuple(state.shape[1:]) != (heads, dim, dim) or proj.stride(1) != 1:
+            raise KernelError("generalized_delta_rule: float32 decays [T, heads * dim] and state [slots, heads, dim, dim]")
+        out = torch.empty((T, m), dtype=torch.float32, device=proj.device)
+        self._call("ember_generalized_delta_rule", proj.data_ptr(), proj.stride(0), int(r_col), int(k_col), int(v_col), int(a_col),
+                   a_bias.data_ptr(), self._dense(wz, "decays").data_ptr(), float(decay_coef), float(unit_eps), state.data_ptr(),
+                   out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.cu_new.data_ptr(), plan.n, heads, dim,
+                   _code(proj.dtype))
+        return out
+
     # ------------------------------------------------------------------ experts by table
     def moe_route(self, tokens, T, table, experts, top):
-        """The step's (token, choice) pairs by expert: (expert of each pair, running counts, pairs in expert order)."""
+        """The step's (token, choice) pairs by expert: (expert of each pair, running counts, pairs in expert order).
+        tokens None: row t of `table` [T, top] is token t's choice (what `moe_pick` made)."""
         pairs = T * top
         buf = torch.empty(2 * pairs + experts + 1, dtype=torch.int32, device=table.device)
         pair_expert, offsets, order = buf[:pairs], buf[pairs:pairs + experts + 1], buf[pairs + experts + 1:]
-        self._call("ember_moe_route", tokens.data_ptr(), table.data_ptr(), T, top, experts, table.shape[0],
+        self._call("ember_moe_route", self._ptr(tokens), table.data_ptr(), T, top, experts, table.shape[0],
                    pair_expert.data_ptr(), offsets.data_ptr(), order.data_ptr())
         return pair_expert, offsets, order, T, top, experts
 
@@ -1173,15 +1280,43 @@ class CudaOps:
             tiled = dtype == torch.bfloat16 and pairs >= MOE_TILE_PAIRS
         return 1 if tiled and k % 8 == 0 and n_out % 2 == 0 else 0
 
-    def moe_gate_up(self, h, w_gate_up, routing, out_dtype, tiled=None):
+    def moe_pick(self, logits, correction, experts, top, groups, keep_groups, route_scale):
+        """The router's choice for every row of float32 logits [T, >= experts]: scores sigmoid(z); chosen on score +
+        correction among the experts of the `keep_groups` groups (of `groups` equal groups of neighbours) whose two
+        largest choice scores add up to the most; weights = the chosen's scores over their sum (+ 1e-20) times
+        `route_scale`.  Returns (chosen int32 [T, top], weights float32 [T, top])."""
+        T = logits.shape[0]
+        if logits.dtype != torch.float32 or logits.shape[1] < experts or correction.dtype != torch.float32 or correction.numel() != experts:
+            raise KernelError("moe_pick: float32 logits of at least `experts` columns and a float32 correction an expert")
+        chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+        weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+        self._call("ember_moe_pick", self._dense(logits, "logits").data_ptr(), logits.shape[1], correction.data_ptr(), T, int(experts),
+                   int(top), int(groups), int(keep_groups), float(route_scale), chosen.data_ptr(), weights.data_ptr())
+        return chosen, weights
+
+    def moe_combine(self, x, y, weights, shared, logits, gate_col):
+        """x + sum_k weights[:, k] * y[:, k, :] (+ shared, times sigmoid(logits[:, gate_col]) where logits are given),
+        float32, as a new tensor."""
+        T, top, width = y.shape
+        if any(t is not None and t.dtype != torch.float32 for t in (x, y, weights, shared, logits)) or tuple(x.shape) != (T, width) \
+                or tuple(weights.shape) != (T, top) or (shared is not None and tuple(shared.shape) != (T, width)):
+            raise KernelError("moe_combine: float32 rows of fitting sizes")
+        out = torch.empty_like(x)
+        self._call("ember_moe_combine", self._dense(x, "stream").data_ptr(), self._dense(y, "experts' rows").data_ptr(),
+                   self._dense(weights, "weights").data_ptr(), self._ptr(None if shared is None else self._dense(shared, "shared rows")),
+                   self._ptr(logits), 0 if logits is None else logits.shape[1], int(gate_col), out.data_ptr(), T, top, width)
+        return out
+
+    def moe_gate_up(self, h, w_gate_up, routing, out_dtype, tiled=None, limit=0.0, alpha=1.0, shift=0.0):
         pair_expert, offsets, order, T, top, experts = routing
         inner, width = w_gate_up.shape[1] // 2, w_gate_up.shape[2]
         if h.dtype != w_gate_up.dtype or out_dtype != h.dtype or h.shape[1] != width or w_gate_up.shape[0] != experts:
             raise KernelError("moe_gate_up: rows, stacked matrices and output of one element type and fitting sizes")
         out = torch.empty((T * top, inner), dtype=out_dtype, device=h.device)
-        self._call("ember_moe_gate_up", self._dense(h, "rows").data_ptr(), self._dense(w_gate_up, "experts").data_ptr(),
+        self._call("ember_moe_gate_up_act", self._dense(h, "rows").data_ptr(), self._dense(w_gate_up, "experts").data_ptr(),
                    pair_expert.data_ptr(), offsets.data_ptr(), order.data_ptr(), out.data_ptr(), T, top, experts, width,
-                   inner, self._moe_tiled(T * top, h.dtype, tiled, width, inner), _code(h.dtype))
+                   inner, self._moe_tiled(T * top, h.dtype, tiled, width, inner), _code(h.dtype), float(limit), float(alpha),
+                   float(shift))
         return out
 
     def moe_down(self, inner_rows, w_down, routing, tiled=None):

@@ -15,6 +15,8 @@
 namespace {
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+// what follows the convolution's sum: silu (act 0) or nothing (act 1)
+__device__ __forceinline__ float conv_act(float v, int act) { return act == 0 ? silu_f(v) : v; }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
 // ---------------------------------------------------------------------------- convolution
@@ -29,7 +31,7 @@ template <typename T, int TMAX>
 __global__ void conv_silu_kernel(const T* __restrict__ in, long long in_stride, int col0, int channels, int taps,
                                  const float* __restrict__ w, const float* __restrict__ bias,
                                  const float* __restrict__ state, T* __restrict__ out, const int* __restrict__ seq_slot,
-                                 const int* __restrict__ seq_start, const int* __restrict__ cu_new, int runs) {
+                                 const int* __restrict__ seq_start, const int* __restrict__ cu_new, int runs, int act) {
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= channels) return;
   const int s = blockIdx.x / runs, run = blockIdx.x % runs;
@@ -66,7 +68,7 @@ __global__ void conv_silu_kernel(const T* __restrict__ in, long long in_stride, 
     float acc = b;
 #pragma unroll
     for (int k = 0; k < TMAX; ++k) acc = fmaf(wt[k], hist[k], acc);
-    out[(size_t)(t0 + i) * channels + c] = from_float<T>(silu_f(acc));
+    out[(size_t)(t0 + i) * channels + c] = from_float<T>(conv_act(acc, act));
 #pragma unroll
     for (int k = 0; k + 1 < TMAX; ++k) hist[k] = hist[k + 1];
   }
@@ -87,7 +89,7 @@ template <typename T, int TMAX>
 __global__ void conv_silu2_kernel(const T* __restrict__ in, long long in_stride, int col0, int channels, int taps,
                                   const float* __restrict__ w, const float* __restrict__ bias,
                                   const float* __restrict__ state, T* __restrict__ out, const int* __restrict__ seq_slot,
-                                  const int* __restrict__ seq_start, const int* __restrict__ cu_new, int runs) {
+                                  const int* __restrict__ seq_start, const int* __restrict__ cu_new, int runs, int act) {
   const int c = 2 * (blockIdx.y * blockDim.x + threadIdx.x);
   if (c >= channels) return;
   const int s = blockIdx.x / runs, run = blockIdx.x % runs;
@@ -127,7 +129,7 @@ __global__ void conv_silu2_kernel(const T* __restrict__ in, long long in_stride,
       a0 = fmaf(wt[k].x, hist[k].x, a0);
       a1 = fmaf(wt[k].y, hist[k].y, a1);
     }
-    store2(out + (size_t)(t0 + i) * channels + c, silu_f(a0), silu_f(a1));
+    store2(out + (size_t)(t0 + i) * channels + c, conv_act(a0, act), conv_act(a1, act));
 #pragma unroll
     for (int k = 0; k + 1 < TMAX; ++k) hist[k] = hist[k + 1];
   }
@@ -162,7 +164,7 @@ __global__ void conv_state_kernel(const T* __restrict__ in, long long in_stride,
 template <typename T>
 __global__ void conv_step_kernel(const T* __restrict__ in, long long in_stride, int col0, int channels, int taps,
                                  const float* __restrict__ w, const float* __restrict__ bias, float* __restrict__ state,
-                                 T* __restrict__ out, const int* __restrict__ seq_slot, const int* __restrict__ seq_start) {
+                                 T* __restrict__ out, const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int act) {
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= channels) return;
   const int t = blockIdx.x;
@@ -183,7 +185,7 @@ __global__ void conv_step_kernel(const T* __restrict__ in, long long in_stride, 
   }
   acc = fmaf(w[(size_t)c * taps + taps - 1], cur, acc);
   if (taps > 1) st[(size_t)(taps - 2) * channels] = cur;
-  *o = from_float<T>(silu_f(acc));
+  *o = from_float<T>(conv_act(acc, act));
 }
 
 // ---------------------------------------------------------------------------- recurrence
@@ -795,10 +797,25 @@ int launch_pieces(const void* xbc, const void* dt_in, long long dt_stride, int d
 
 // all_single: every sequence brings one token (token t is sequence t): one launch does the state's shift too.
 // max_new: the most tokens one sequence brings (the launch is sized by it).
+EMBER_API int ember_conv_act(const void* in, long long in_stride, int col0, int channels, int taps, const float* w,
+                             const float* bias, float* state, void* out, const int* token_seq, const int* seq_slot,
+                             const int* seq_start, const int* cu_new, int T, int n_seqs, int max_new, int all_single,
+                             int dtype, int act, cudaStream_t stream);
+
 EMBER_API int ember_conv_silu(const void* in, long long in_stride, int col0, int channels, int taps, const float* w,
                               const float* bias, float* state, void* out, const int* token_seq, const int* seq_slot,
                               const int* seq_start, const int* cu_new, int T, int n_seqs, int max_new, int all_single,
                               int dtype, cudaStream_t stream) {
+  return ember_conv_act(in, in_stride, col0, channels, taps, w, bias, state, out, token_seq, seq_slot, seq_start, cu_new, T,
+                        n_seqs, max_new, all_single, dtype, 0, stream);
+}
+
+// The same with what follows the convolution's sum as an argument: act 0 silu, 1 nothing.
+EMBER_API int ember_conv_act(const void* in, long long in_stride, int col0, int channels, int taps, const float* w,
+                             const float* bias, float* state, void* out, const int* token_seq, const int* seq_slot,
+                             const int* seq_start, const int* cu_new, int T, int n_seqs, int max_new, int all_single,
+                             int dtype, int act, cudaStream_t stream) {
+  EMBER_CHECK(act == 0 || act == 1, "conv: activation %d", act);
   EMBER_CHECK(T > 0 && n_seqs > 0 && channels > 0 && taps >= 1 && taps <= 16, "conv_silu: bad sizes");
   EMBER_CHECK(taps == 1 || state != nullptr, "conv_silu: a convolution of %d taps carries state", taps);
   EMBER_CHECK(dtype == EMBER_F32 || dtype == EMBER_BF16, "conv_silu: element type %d", dtype);
@@ -813,16 +830,16 @@ EMBER_API int ember_conv_silu(const void* in, long long in_stride, int col0, int
   do {                                                                                                                    \
     if (all_single && T == n_seqs) {                                                                                      \
       launch_plain(conv_step_kernel<TT>, dim3(T, bx), dim3(128), 0, stream, (const TT*)in, in_stride, col0, channels, taps, \
-                 w, bias, state, (TT*)out, seq_slot, seq_start);                                                          \
+                 w, bias, state, (TT*)out, seq_slot, seq_start, act);                                                          \
     } else if (taps <= 4 && pairs) {                                                                                      \
       conv_silu2_kernel<TT, 4><<<dim3(n_seqs * runs, (channels / 2 + 127) / 128), 128, 0, stream>>>(                      \
-          (const TT*)in, in_stride, col0, channels, taps, w, bias, state, (TT*)out, seq_slot, seq_start, cu_new, runs);   \
+          (const TT*)in, in_stride, col0, channels, taps, w, bias, state, (TT*)out, seq_slot, seq_start, cu_new, runs, act);   \
     } else if (taps <= 4) {                                                                                               \
       conv_silu_kernel<TT, 4><<<dim3(n_seqs * runs, bx), 128, 0, stream>>>(                                               \
-          (const TT*)in, in_stride, col0, channels, taps, w, bias, state, (TT*)out, seq_slot, seq_start, cu_new, runs);   \
+          (const TT*)in, in_stride, col0, channels, taps, w, bias, state, (TT*)out, seq_slot, seq_start, cu_new, runs, act);   \
     } else {                                                                                                              \
       conv_silu_kernel<TT, 16><<<dim3(n_seqs * runs, bx), 128, 0, stream>>>(                                              \
-          (const TT*)in, in_stride, col0, channels, taps, w, bias, state, (TT*)out, seq_slot, seq_start, cu_new, runs);   \
+          (const TT*)in, in_stride, col0, channels, taps, w, bias, state, (TT*)out, seq_slot, seq_start, cu_new, runs, act);   \
     }                                                                                                                     \
     if (!(all_single && T == n_seqs)) {                                                                                   \
       if (taps > 1)                                                                                                       \

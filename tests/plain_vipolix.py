@@ -256,3 +256,11 @@ def forward(cfg, W, tokens, per_layer=False):
         streams.append(x.copy())
     logits = norm_around_zero(x, W["final.norm"], eps) @ W["head"].T
     return (logits, np.stack(streams)) if per_layer else logits
+
+
+def generate(cfg, W, prompt, steps):
+    """Greedy continuation: the first of the largest logits, `steps` times."""
+    ids = list(prompt)
+    for _ in range(steps):
+        ids.append(int(np.argmax(forward(cfg, W, ids)[-1])))
+    return ids[len(prompt):]
