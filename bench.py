@@ -239,6 +239,35 @@ SOSUTAR_SIZES = {
 }
 
 
+VIPOLIX_SIZES = {
+    # gated linear attention: heads / key size / value size; the generalized delta rule: heads / size; taps of the attention's
+    # convolutions, its rotated dimensions; groups of experts / kept; values a layer of the per-layer token input
+    "small": dict(g_heads=16, g_dim=64, g_vdim=64, d_heads=16, d_dim=64, conv=4, rot=32, groups=4, keep=2, side=64),
+    "medium": dict(g_heads=16, g_dim=128, g_vdim=128, d_heads=16, d_dim=128, conv=4, rot=64, groups=4, keep=2, side=128),
+}
+
+
+def vipolix_config(size: str):
+    """A Vipolix of the width, layer count, attention heads, chunk (the others' window), experts and vocabulary of
+    `DESIGN_SIZES[size]`: layers of gated linear attention and of attention beside the generalized delta rule in turn, every
+    one with routed experts and a shared expert."""
+    z, m = DESIGN_SIZES[size], VIPOLIX_SIZES[size]
+    left = {"dim": z["dim"], "vdim": z["dim"], "heads": z["heads"], "kv_heads": z["kv_heads"], "scale": z["dim"] ** -0.5,
+            "conv": m["conv"], "mask": {"size": z["window"]}, "rot": {"dims": m["rot"], "base": 500000.0}}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5, "groups": {"count": m["groups"], "keep": m["keep"]}},
+           "shared": {"ff": z["shared_ff"], "limit": 7.0}}
+    layers = []
+    for i in range(z["layers"]):
+        if i % 2 == 0:
+            layers.append({"type": "gla", "mixer": {"heads": m["g_heads"], "dim": m["g_dim"], "vdim": m["g_vdim"], "tau": 16.0}, "mlp": dict(moe)})
+        else:
+            layers.append({"type": "parallel", "mixer": {"left": dict(left), "right": {"heads": m["d_heads"], "dim": m["d_dim"]},
+                                                         "left_scale": 1.0, "right_scale": 1.0}, "mlp": dict(moe)})
+    return {"architecture": "Vipolix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "token_side": {"dim": m["side"]},
+            "layers": layers}
+
+
 def sosutar_config(size: str):
     """A Sosutar of the width, layer count, attention heads, window, dense inner size and vocabulary of `DESIGN_SIZES[size]`:
     an mLSTM layer without a feed-forward, layers of attention beside a minGRU with a feed-forward, and a last mLSTM layer
@@ -285,6 +314,8 @@ def design_configs(size: str, design: str = "nipolorn"):
         return (muzozen_config(size),) + design_configs(size)
     if design == "sosutar":
         return (sosutar_config(size),) + design_configs(size)
+    if design == "vipolix":
+        return (vipolix_config(size),) + design_configs(size)
     z = DESIGN_SIZES[size]
     left = {"dim": z["dim"], "vdim": z["dim"], "heads": z["heads"], "kv_heads": z["kv_heads"], "scale": z["dim"] ** -0.5,
             "mask": {"size": z["window"], "keep_first": z["keep"]}}
@@ -418,7 +449,7 @@ def main() -> int:
                     help="time one bfloat16 product on every kernel that takes it, instead of the benchmark")
     ap.add_argument("--act", default=None, choices=[None, "gelu_tanh", "gelu_erf"], help="with --linear: the epilogue's activation")
     ap.add_argument("--residual", action="store_true", help="with --linear: add a float32 residual (the output is float32 then)")
-    ap.add_argument("--design", default=None, choices=["nipolorn", "muzozen", "sosutar"],
+    ap.add_argument("--design", default=None, choices=["nipolorn", "muzozen", "sosutar", "vipolix"],
                     help="instead of the benchmark: prefill and decode throughput of this design beside a GPT-2 of equal size "
                          "(muzozen: beside a Nipolorn and a GPT-2 of equal size)")
     ap.add_argument("--design-size", default="medium", choices=sorted(DESIGN_SIZES), help="with --design: the layers' sizes")

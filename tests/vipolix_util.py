@@ -63,7 +63,7 @@ CONFIGS = {
         _parallel(LEFT_C, 12, 2, (1.5, 1.0), _moe(5, 2, 14, 2.0, 3.0))]},
 }
 SEEDS = {"vip_a": 3, "vip_b": 4, "vip_c": 5}
-TOL = {"float32": 2e-4, "bfloat16": 6e-2}
+TOL = {"float32": 1e-4, "bfloat16": 8e-2}
 
 
 def config(name: str) -> dict:
@@ -97,6 +97,16 @@ def write_model(folder: str, cfg: dict, seed: int, scale_up: float = 6.0) -> str
 
 def ids(seed: int, vocab: int, n: int) -> list:
     return np.random.default_rng(seed).integers(0, vocab, n).tolist()
+
+
+def rows_agree(got, ref, dtype: str) -> bool:
+    """`got` against the plain model's `ref` (lists of [rows, vocab] arrays).  In 32-bit every row is within TOL.  In
+    bfloat16 a rounding can turn a near tie of the router's choice the other way, and the token then runs another expert
+    than the plain model's: a few rows may differ by more (at most one in ten), the typical row must not."""
+    errors = np.array([row_error(g[i], r[i]) for g, r in zip(got, ref) for i in range(len(r))])
+    if dtype == "float32":
+        return bool(errors.max() < TOL[dtype])
+    return bool((errors >= TOL[dtype]).mean() <= 0.1 and np.median(errors) < TOL[dtype] / 2)
 
 
 def row_error(got, ref) -> float:
