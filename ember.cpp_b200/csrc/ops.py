@@ -25,8 +25,8 @@ _c_int, _c_float, _c_void, _c_size, _c_u64 = ctypes.c_int, ctypes.c_float, ctype
 
 _SIGNATURES = {
     "ember_token_shift": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
-    "ember_side_input": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void,
-                         _c_void, _c_float, _c_int, _c_int, _c_int, _c_void],
+    "ember_cast_rows": [_c_void, _c_void, _c_size, _c_int, _c_void],
+    "ember_table_gate": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_low_rank_out": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int,
                            _c_void],
     "ember_gla_scan": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_void, _c_float, _c_void, _c_void, _c_void, _c_void,
@@ -1210,17 +1210,24 @@ class CudaOps:
         return out
 
     def side_input(self, x, plan, table, col, dim, w_gate, w_proj, w_norm, eps):
-        """x + unit_rms(W_proj (gelu_tanh(W_gate x) * e)) * w_norm, e = `dim` columns from `col` of each token's row of
-        `table`; float32 rows in, a new float32 tensor out."""
+        """x += unit_rms(W_proj (gelu_tanh(W_gate x) * e)) * w_norm in place, e = `dim` columns from `col` of each token's
+        row of `table`: the stream's rows in the compute type, the first product with its GELU, the table's values, the
+        second product with float32 sums, and the norm with the sum (`add_normed`)."""
         T, width = x.shape
-        if x.dtype != torch.float32 or table.dtype != w_gate.dtype or w_proj.dtype != w_gate.dtype or \
+        dtype = w_gate.dtype
+        if x.dtype != torch.float32 or table.dtype != dtype or w_proj.dtype != dtype or \
                 tuple(w_gate.shape) != (dim, width) or tuple(w_proj.shape) != (width, dim) or w_norm.numel() != width:
             raise KernelError("side_input: a float32 stream, the table and both matrices of one element type and fitting sizes")
-        out = torch.empty_like(x)
-        self._call("ember_side_input", self._dense(x, "stream").data_ptr(), out.data_ptr(), plan.tokens.data_ptr(),
-                   plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), table.data_ptr(), table.shape[0], table.shape[1], int(col),
-                   int(dim), w_gate.data_ptr(), w_proj.data_ptr(), w_norm.data_ptr(), float(eps), T, width, _code(w_gate.dtype))
-        return out
+        rows = self._dense(x, "stream")
+        if dtype != torch.float32:
+            rows = torch.empty((T, width), dtype=dtype, device=x.device)
+            self._call("ember_cast_rows", x.data_ptr(), rows.data_ptr(), T * width, _code(dtype))
+        z = self.linear(rows, w_gate, None, act="gelu_tanh", out_dtype=dtype)
+        g = torch.empty_like(z)
+        self._call("ember_table_gate", z.data_ptr(), g.data_ptr(), plan.tokens.data_ptr(), table.data_ptr(), table.shape[0],
+                   table.shape[1], int(col), int(dim), T, _code(dtype))
+        y = self.linear(g, w_proj, None, out_dtype=torch.float32)
+        return self.add_normed(x, [(y, 1.0)], w_norm, eps)
 
     # ------------------------------------------------------------------ linear attention, the generalized delta rule
     def low_rank_out(self, proj, col, w2, bias, act):

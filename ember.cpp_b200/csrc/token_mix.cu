@@ -4,24 +4,14 @@
 //                 the slot's carried row (zeros at position 0); the slot then carries the sequence's last row of
 //                 the step.  The block of a sequence's first token does both: it reads the carried row and, having
 //                 read it, writes the new one, so no other block touches the slot's row.
-//   side_input    x[t] += unit_rms(W_proj (gelu_tanh(W_gate x[t]) * e[t])) * w, e[t] = `dim` columns from `col` of
-//                 the token's row of a table; one block a token, float32 arithmetic, sums in a fixed order.
+//   cast_rows     rows of the float32 stream in the compute type (what a product reads)
+//   table_gate    g[t, d] = z[t, d] * e[t, d], e[t] = `dim` columns from `col` of the token's row of a table: the
+//                 per-layer input from the token ids, between its two products
 #include "common.cuh"
 
 namespace {
 
 constexpr int kThreads = 256;
-
-__device__ __forceinline__ float block_sum(float v, float* red) {
-  v = warp_sum(v);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  __syncthreads();
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float total = 0.f;
-  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) total += red[w];
-  return total;
-}
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
@@ -57,47 +47,21 @@ token_shift_kernel(const T* __restrict__ h, T* __restrict__ out, const float* __
   }
 }
 
-// dynamic shared memory: width + dim floats
 template <typename T>
-__global__ void __launch_bounds__(kThreads)
-side_input_kernel(const float* __restrict__ x, float* __restrict__ out, const int* __restrict__ tokens,
-                  const int* __restrict__ token_seq, const int* __restrict__ seq_slot, const T* __restrict__ table,
-                  int vocab, int table_width, int col, int dim, const T* __restrict__ w_gate, const T* __restrict__ w_proj,
-                  const float* __restrict__ w_norm, float eps, int width) {
-  extern __shared__ float sm[];
-  __shared__ float red[kThreads / 32];
-  float* xs = sm;            // the token's row of the stream, then y
-  float* g = sm + width;
+__global__ void cast_rows_kernel(const float* __restrict__ x, T* __restrict__ out, size_t total) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_float<T>(x[i]);
+}
+
+// grid (T)
+template <typename T>
+__global__ void table_gate_kernel(const T* __restrict__ z, T* __restrict__ out, const int* __restrict__ tokens,
+                                  const T* __restrict__ table, int vocab, int table_width, int col, int dim) {
   const int t = blockIdx.x;
-  const float* row = x + (size_t)t * width;
-  float* o = out + (size_t)t * width;
-  if (seq_slot[token_seq[t]] < 0) {
-    for (int c = threadIdx.x; c < width; c += kThreads) o[c] = row[c];
-    return;
-  }
-  for (int c = threadIdx.x; c < width; c += kThreads) xs[c] = row[c];
-  __syncthreads();
   const int tok = min(max(tokens[t], 0), vocab - 1);
   const T* e = table + (size_t)tok * table_width + col;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int d = warp; d < dim; d += kThreads / 32) {
-    const T* w = w_gate + (size_t)d * width;
-    float acc = 0.f;
-    for (int c = lane; c < width; c += 32) acc = fmaf(to_float(w[c]), xs[c], acc);
-    acc = warp_sum(acc);
-    if (lane == 0) g[d] = gelu_tanh(acc) * to_float(e[d]);
-  }
-  __syncthreads();
-  float ss = 0.f;
-  for (int c = threadIdx.x; c < width; c += kThreads) {
-    const T* w = w_proj + (size_t)c * dim;
-    float acc = 0.f;
-    for (int d = 0; d < dim; ++d) acc = fmaf(to_float(w[d]), g[d], acc);
-    xs[c] = acc;     // (a thread reads and writes its own columns only)
-    ss = fmaf(acc, acc, ss);
-  }
-  const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
-  for (int c = threadIdx.x; c < width; c += kThreads) o[c] = row[c] + xs[c] * inv * w_norm[c];
+  for (int d = threadIdx.x; d < dim; d += blockDim.x)
+    out[(size_t)t * dim + d] = from_float<T>(to_float(z[(size_t)t * dim + d]) * to_float(e[d]));
 }
 
 }  // namespace
@@ -120,25 +84,36 @@ EMBER_API int ember_token_shift(const void* h, void* out, const float* mu, float
   return 0;
 }
 
-// x, out float32 [T, width]; table [vocab, table_width], w_gate [dim, width], w_proj [width, dim] (dtype); w_norm float32 [width].
-EMBER_API int ember_side_input(const float* x, float* out, const int* tokens, const int* token_seq, const int* seq_slot,
-                               const void* table, int vocab, int table_width, int col, int dim, const void* w_gate,
-                               const void* w_proj, const float* w_norm, float eps, int T, int width, int dtype,
-                               cudaStream_t stream) {
-  EMBER_CHECK(T > 0 && width > 0 && vocab > 0 && dim >= 1 && col >= 0 && col + dim <= table_width,
-              "side_input: %d tokens, width %d, columns %d..%d of %d", T, width, col, col + dim, table_width);
-  const size_t smem = (size_t)(width + dim) * sizeof(float);
-  EMBER_CHECK(smem <= 48 * 1024, "side_input: width %d + %d values exceed a block's shared memory", width, dim);
+// x float32 [n], out [n] (dtype)
+EMBER_API int ember_cast_rows(const float* x, void* out, size_t n, int dtype, cudaStream_t stream) {
+  EMBER_CHECK(n > 0, "cast_rows: nothing to do");
+  const unsigned grid = (unsigned)((n + 1023) / 1024 < 2048 ? (n + 1023) / 1024 : 2048);
   cudaError_t e;
   if (dtype == EMBER_F32)
-    e = launch_plain(side_input_kernel<float>, dim3(T), dim3(kThreads), smem, stream, x, out, tokens, token_seq, seq_slot,
-                     (const float*)table, vocab, table_width, col, dim, (const float*)w_gate, (const float*)w_proj, w_norm, eps, width);
+    e = launch_plain(cast_rows_kernel<float>, dim3(grid), dim3(256), 0, stream, x, (float*)out, n);
   else if (dtype == EMBER_BF16)
-    e = launch_plain(side_input_kernel<__nv_bfloat16>, dim3(T), dim3(kThreads), smem, stream, x, out, tokens, token_seq, seq_slot,
-                     (const __nv_bfloat16*)table, vocab, table_width, col, dim, (const __nv_bfloat16*)w_gate,
-                     (const __nv_bfloat16*)w_proj, w_norm, eps, width);
+    e = launch_plain(cast_rows_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, x, (__nv_bfloat16*)out, n);
   else
-    return ember_fail("side_input: element type %d", dtype);
-  if (e != cudaSuccess) return ember_fail("side_input: %s", cudaGetErrorString(e));
+    return ember_fail("cast_rows: element type %d", dtype);
+  if (e != cudaSuccess) return ember_fail("cast_rows: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+// z, out [T, dim]; table [vocab, table_width] (all dtype); tokens int32 [T]
+EMBER_API int ember_table_gate(const void* z, void* out, const int* tokens, const void* table, int vocab, int table_width,
+                               int col, int dim, int T, int dtype, cudaStream_t stream) {
+  EMBER_CHECK(T > 0 && vocab > 0 && dim >= 1 && col >= 0 && col + dim <= table_width, "table_gate: %d tokens, columns %d..%d of %d",
+              T, col, col + dim, table_width);
+  const int threads = dim <= 32 ? 32 : dim <= 64 ? 64 : 128;
+  cudaError_t e;
+  if (dtype == EMBER_F32)
+    e = launch_plain(table_gate_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)z, (float*)out, tokens,
+                     (const float*)table, vocab, table_width, col, dim);
+  else if (dtype == EMBER_BF16)
+    e = launch_plain(table_gate_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)z,
+                     (__nv_bfloat16*)out, tokens, (const __nv_bfloat16*)table, vocab, table_width, col, dim);
+  else
+    return ember_fail("table_gate: element type %d", dtype);
+  if (e != cudaSuccess) return ember_fail("table_gate: %s", cudaGetErrorString(e));
   return 0;
 }

@@ -100,8 +100,13 @@ class ParallelMixers(Mixer):
         return out
 
     def forward(self, ctx, h, residual, app):
+        branches = self.branches(ctx, h, app)
+        add = getattr(ctx.ops, "add_branches", None)
+        if add is not None and len(branches) <= 8:      # the weighted sum (members' own norms included) and the stream's, one launch
+            return add(residual, [(b[0], b[1], b[2][0] if len(b) > 2 and b[2] is not None else None) for b in branches],
+                       None, self.eps)
         x = residual
-        for rows, f in plain_branches(ctx, self.branches(ctx, h, app)):
+        for rows, f in plain_branches(ctx, branches):
             x = x + f * rows
         return x
 

@@ -138,7 +138,8 @@ def test_the_stream_after_every_layer(folders, plains):
     seen = []
     for block in eng.model.blocks:
         inner = block.forward
-        block.forward = lambda ctx, x, app, inner=inner: seen.append(inner(ctx, x, app)) or seen[-1]
+        # (a copy: the next layer may add into the stream in place)
+        block.forward = lambda ctx, x, app, inner=inner: (lambda y: seen.append(y.clone()) or y)(inner(ctx, x, app))
     slot = eng.open()
     eng.step([(slot, seq, [30])])
     for got, want in zip(seen, streams):
