@@ -30,9 +30,10 @@ _SIGNATURES = {
     "ember_low_rank_out": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int,
                            _c_void],
     "ember_gla_scan": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_void, _c_float, _c_void, _c_void, _c_void, _c_void,
-                       _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
+                       _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
     "ember_generalized_delta_rule": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_float,
-                                     _c_float, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
+                                     _c_float, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void,
+                                     _c_int, _c_void],
     "ember_moe_pick": [_c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void, _c_void, _c_void],
     "ember_moe_combine": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_int, _c_int, _c_void],
     "ember_moe_gate_up_act": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -190,6 +191,10 @@ def load_library() -> ctypes.CDLL:
     lib.ember_wait_probe.restype = _c_int
     lib.ember_set_option.argtypes = [_c_int, _c_int]
     lib.ember_set_option.restype = _c_int
+    lib.ember_recurrence_piece.argtypes = []
+    lib.ember_recurrence_piece.restype = _c_int
+    lib.ember_recurrence_scratch.argtypes = [_c_int] * 6
+    lib.ember_recurrence_scratch.restype = _c_size
     lib.ember_attention_decode_partials.argtypes = [_c_int] * 5
     lib.ember_attention_decode_partials.restype = _c_size
     lib.ember_ssd_scan_piece.argtypes = []
@@ -1232,17 +1237,32 @@ class CudaOps:
     # ------------------------------------------------------------------ linear attention, the generalized delta rule
     def low_rank_out(self, proj, col, w2, bias, act):
         """bias + act(proj[:, col : col + rank]) W2^T with float32 sums: the second half of a product of low rank;
-        w2 float32 [n_out, rank], act "none" or "tanh".  float32 [T, n_out]."""
-        n_out, rank = w2.shape
+        w2 float32 [rank, n_out] (W2 transposed: the kernel reads an output's weights across its rows), act "none" or
+        "tanh".  float32 [T, n_out]."""
+        rank, n_out = w2.shape
         if act not in ("none", "tanh") or w2.dtype != torch.float32 or bias.dtype != torch.float32 or bias.numel() != n_out \
                 or col + rank > proj.shape[1] or proj.stride(1) != 1:
-            raise KernelError("low_rank_out: float32 [outputs, rank] and bias, the rank's columns inside the rows")
+            raise KernelError("low_rank_out: float32 [rank, outputs] and bias, the rank's columns inside the rows")
         out = torch.empty((proj.shape[0], n_out), dtype=torch.float32, device=proj.device)
-        self._call("ember_low_rank_out", proj.data_ptr(), proj.stride(0), int(col), rank, w2.data_ptr(), bias.data_ptr(),
+        self._call("ember_low_rank_out", proj.data_ptr(), proj.stride(0), int(col), rank, self._dense(w2, "w2").data_ptr(), bias.data_ptr(),
                    out.data_ptr(), proj.shape[0], n_out, 1 if act == "tanh" else 0, _code(proj.dtype))
         return out
 
-    def gla_scan(self, proj, q_col, k_col, v_col, z, tau, state, plan, heads, dim, vdim):
+    RECURRENCE_PIECES_FROM = 256    # new tokens of a step's longest sequence from which a recurrence is walked in pieces
+
+    def _recurrence_pieces(self, rule, plan, heads, dim, vdim, pieces, device):
+        """(count of pieces, scratch) for a walk of gated linear attention (rule 0) or the generalized delta rule (1):
+        sequences that bring many tokens are cut into pieces that are walked side by side.  pieces: None chooses, 0
+        forces one walk, a count forces pieces (the tests')."""
+        if pieces is None:
+            pieces = 0 if plan.all_single or plan.max_new < self.RECURRENCE_PIECES_FROM else 1
+        if not pieces:
+            return 0, None
+        count = -(-max(int(plan.max_new), 1) // self.lib.ember_recurrence_piece())
+        floats = self.lib.ember_recurrence_scratch(rule, plan.n, count, heads, dim, vdim)
+        return count, torch.empty(floats, dtype=torch.float32, device=device)
+
+    def gla_scan(self, proj, q_col, k_col, v_col, z, tau, state, plan, heads, dim, vdim, pieces=None):
         """Gated linear attention token by token: S <- diag(sigmoid(z)^(1/tau)) S + k v^T, o = S^T (q dim^(-1/2)); q, k, v
         from columns of `proj`, z float32 [T, heads * dim], state float32 [slots, heads, dim, vdim].  float32 [T, heads * vdim]."""
         T = proj.shape[0]
@@ -1250,12 +1270,15 @@ class CudaOps:
                 tuple(state.shape[1:]) != (heads, dim, vdim) or proj.stride(1) != 1:
             raise KernelError("gla_scan: float32 decays [T, heads * dim] and state [slots, heads, dim, vdim]")
         out = torch.empty((T, heads * vdim), dtype=torch.float32, device=proj.device)
+        count, scratch = self._recurrence_pieces(0, plan, heads, dim, vdim, pieces, proj.device)
         self._call("ember_gla_scan", proj.data_ptr(), proj.stride(0), int(q_col), int(k_col), int(v_col), self._dense(z, "z").data_ptr(),
                    float(tau), state.data_ptr(), out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(),
-                   plan.cu_new.data_ptr(), plan.n, heads, dim, vdim, _code(proj.dtype))
+                   plan.cu_new.data_ptr(), plan.n, heads, dim, vdim, count, self._ptr(scratch), _code(proj.dtype))
+        self.launches += 2 if count else 0       # (the carry kernel and the second walk)
         return out
 
-    def generalized_delta_rule(self, proj, r_col, k_col, v_col, a_col, a_bias, wz, decay_coef, state, plan, heads, dim, unit_eps):
+    def generalized_delta_rule(self, proj, r_col, k_col, v_col, a_col, a_bias, wz, decay_coef, state, plan, heads, dim, unit_eps,
+                               pieces=None):
         """S <- diag(w) S - (a u)(u^T S) + k v^T, o = S^T r, with w = exp(-decay_coef * sigmoid(wz)), a = sigmoid(a_in +
         a_bias), u the unit key; r, k, v, a_in from columns of `proj`, wz float32 [T, heads * dim], state float32
         [slots, heads, dim, dim].  float32 [T, heads * dim]."""
@@ -1264,10 +1287,12 @@ class CudaOps:
                 tuple(state.shape[1:]) != (heads, dim, dim) or proj.stride(1) != 1:
             raise KernelError("generalized_delta_rule: float32 decays [T, heads * dim] and state [slots, heads, dim, dim]")
         out = torch.empty((T, m), dtype=torch.float32, device=proj.device)
+        count, scratch = self._recurrence_pieces(1, plan, heads, dim, dim, pieces, proj.device)
         self._call("ember_generalized_delta_rule", proj.data_ptr(), proj.stride(0), int(r_col), int(k_col), int(v_col), int(a_col),
                    a_bias.data_ptr(), self._dense(wz, "decays").data_ptr(), float(decay_coef), float(unit_eps), state.data_ptr(),
                    out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.cu_new.data_ptr(), plan.n, heads, dim,
-                   _code(proj.dtype))
+                   count, self._ptr(scratch), _code(proj.dtype))
+        self.launches += 2 if count else 0
         return out
 
     # ------------------------------------------------------------------ experts by table

@@ -165,7 +165,7 @@ class GeneralizedDeltaRule(Mixer):
             w = torch.cat([w, torch.zeros((pad, self.width), dtype=w.dtype, device=w.device)])
         self.w_in = w.contiguous()
         self.w_out = runtime.matrix(get(n["out"]))
-        self.w_w2 = runtime.vector(get(n["w2"]))                   # float32 [heads * dim, rank]
+        self.w_w2 = runtime.vector(get(n["w2"])).t().contiguous()  # float32 [rank, heads * dim]: transposed
         self.w0 = runtime.vector(get(n["w0"]))
         self.b_a = runtime.vector(get(n["a"] + self.bias_suffix))
         self.norm_w = runtime.vector(get(n["norm"]))

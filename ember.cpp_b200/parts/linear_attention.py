@@ -65,7 +65,7 @@ class GatedLinearAttention(Mixer):
             w = torch.cat([w, torch.zeros((pad, self.width), dtype=w.dtype, device=w.device)])
         self.w_in = w.contiguous()
         self.w_out = runtime.matrix(get(n["out"]))
-        self.w_a2 = runtime.vector(get(n["a2"]))                                  # float32 [heads * dim, rank]
+        self.w_a2 = runtime.vector(get(n["a2"])).t().contiguous()                 # float32 [rank, heads * dim]: transposed
         self.b_a2 = runtime.vector(get(n["a2"] + self.bias_suffix))
         self.norm_w = runtime.vector(get(n["norm"])).repeat(self.heads).contiguous()     # the heads share the gain
 

@@ -408,10 +408,10 @@ class CpuOps:
         return out.to(h.dtype)
 
     def low_rank_out(self, proj, col, w2, bias, act):
-        lr = proj[:, col:col + w2.shape[1]].float()
+        lr = proj[:, col:col + w2.shape[0]].float()       # (w2 is [rank, outputs])
         if act == "tanh":
             lr = torch.tanh(lr)
-        return lr @ w2.t() + bias
+        return lr @ w2 + bias
 
     def gla_scan(self, proj, q_col, k_col, v_col, z, tau, state, plan, heads, dim, vdim):
         out = torch.zeros(proj.shape[0], heads * vdim)

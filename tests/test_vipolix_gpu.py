@@ -123,7 +123,7 @@ def test_gated_linear_attention_over_steps(ops, dtype, heads, dim, vdim, tau):
     state = torch.full((6, heads, dim, vdim), float("nan"), device="cuda")
 
     def step(plan, rows):
-        z = ops.low_rank_out(rows, 2 * qk + 2 * inner, w2.cuda(), bias.cuda(), "none")
+        z = ops.low_rank_out(rows, 2 * qk + 2 * inner, w2.t().contiguous().cuda(), bias.cuda(), "none")
         o = ops.gla_scan(rows, 0, qk, 2 * qk, z, tau, state, plan, heads, dim, vdim)
         return ops.gated_group_norm(o, rows, 2 * qk + inner, norm_w.repeat(heads).cuda(), heads, eps, dt, gate_first=False)
     got = feed(step, data, dt, width)
@@ -149,7 +149,7 @@ def test_the_generalized_delta_rule_over_steps(ops, dtype, heads, dim):
     state = torch.full((6, heads, dim, dim), float("nan"), device="cuda")
 
     def step(plan, rows):
-        wz = ops.low_rank_out(rows, 5 * m, w2.cuda(), w0.cuda(), "tanh")
+        wz = ops.low_rank_out(rows, 5 * m, w2.t().contiguous().cuda(), w0.cuda(), "tanh")
         o = ops.generalized_delta_rule(rows, 0, m, 2 * m, 4 * m, a_bias.cuda(), wz, coef, state, plan, heads, dim, 1e-6)
         return ops.gated_group_norm(o, rows, 3 * m, norm_w.cuda(), heads, eps, dt, gate_first=False, gate="sigmoid")
     got = feed(step, data, dt, width)
@@ -162,6 +162,36 @@ def test_the_generalized_delta_rule_over_steps(ops, dtype, heads, dim):
         want = P.unit_rms(o, eps).reshape(n, m) * f64(norm_w) * P.sigmoid(x[:, 3 * m:4 * m])
         close(got[s], want, OP_TOL[dtype])
         close(state[s], S, 3e-5 if dtype == "float32" else 1e-4)
+
+
+@pytest.mark.parametrize("rule", ["gla", "delta"])
+@pytest.mark.parametrize("heads, dim, vdim", [(2, 16, 24), (1, 40, 72), (3, 64, 64), (1, 136, 8)])
+def test_a_walk_in_pieces_equals_one_walk(ops, rule, heads, dim, vdim):
+    """Sequences of 300, 129, 5 and 128 new tokens (and a padding sequence) on top of a carried state: every piece from
+    zeros with its transition, the carry, every piece from its start state; against the same step in one walk."""
+    if rule == "delta":
+        vdim = dim
+    m, inner = heads * dim, heads * vdim
+    news, slots, held = [300, 129, 5, 1, 128], [2, 0, 3, -1, 1], [7, 0, 64, 0, 200]
+    T = sum(news)
+    rows = rnd(1, T, 3 * m + inner + 2)                   # q | k | a | v and columns that no one reads
+    z, a_bias = rnd(2, T, m, scale=2.0) + (3.0 if rule == "gla" else 0.0), rnd(3, m)
+    plan = plan_of([(s, h, n) for s, h, n in zip(slots, held, news)])
+    results = []
+    for pieces in (0, 1):
+        state = rnd(4, 5, heads, dim, vdim).cuda()
+        if rule == "gla":
+            out = ops.gla_scan(rows.cuda(), 0, m, 3 * m, z.cuda(), 3.0, state, plan, heads, dim, vdim, pieces=pieces)
+        else:
+            out = ops.generalized_delta_rule(rows.cuda(), 0, m, 3 * m, 2 * m, a_bias.cuda(), z.cuda(), math.exp(-0.5), state, plan,
+                                             heads, dim, 1e-6, pieces=pieces)
+        results.append((out.cpu(), state.cpu()))
+    (out_a, state_a), (out_b, state_b) = results
+    live = torch.cat([torch.full((n,), s >= 0) for s, n in zip(slots, news)])
+    close(out_b[live], f64(out_a[live]), 1e-4)
+    assert not out_b[~live].any()
+    close(state_b, f64(state_a), 1e-4)
+    assert torch.equal(state_b[4], state_a[4])            # a slot that the step does not name keeps its rows
 
 
 def test_linear_attention_keeps_a_token_from_far_back(ops):
@@ -455,6 +485,21 @@ def test_long_decoding_past_many_chunks_with_slots_used_again(folders, plains, d
             for t in state.values():
                 t.fill_(float("nan"))
     assert max(g.pages.size for g in eng.cache.groups) == 6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_takes_the_recurrences_in_pieces(folders, plains, dtype):
+    for name in ("vip_a", "vip_c"):
+        eng, (cfg, W) = E.Engine.from_folder(folders[name], dtype=dtype, max_tokens=1024), plains[name]
+        seq = U.ids(77, cfg["vocab"], 512)
+        got, _ = run_batch(eng, [seq], [511])
+        assert U.rows_agree(got, [P.forward(cfg, W, seq)], dtype)
+        slot, at, rows = eng.open(), 0, []
+        for n in (100, 300, 112):                             # a portion in pieces on top of a carried state
+            rows.append(eng.step([(slot, seq[at:at + n], list(range(n)))]).cpu().numpy())
+            at += n
+        eng.close(slot)
+        assert U.rows_agree([np.concatenate(rows)], [P.forward(cfg, W, seq)], dtype)
 
 
 def test_graph_replay_equals_launch_by_launch(folders):
