@@ -242,9 +242,9 @@ __global__ void __launch_bounds__(256)
 carry_matrix_kernel(const float* __restrict__ local_states, float* __restrict__ start_states, float* __restrict__ state,
                     const int* __restrict__ seq_slot, const int* __restrict__ seq_start, const int* __restrict__ cu_new,
                     int heads, int D, int V, int pieces) {
-  extern __shared__ float carry_sm[];
+  extern __shared__ __align__(16) float carry_sm[];
   float* cols = carry_sm;                          // [D][kCarryColumns]: the current columns, row e at cols[e * 16 ..]
-  float* sM = carry_sm + D * kCarryColumns;        // [D][33]: 32 columns of M
+  float* sM = carry_sm + D * kCarryColumns;        // [D][36]: 32 columns of M (rows start on 16 bytes, apart in the banks)
   const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   const int jj = tid % kCarryColumns, d0 = tid / kCarryColumns;
   const int j = blockIdx.z * kCarryColumns + jj;
@@ -278,16 +278,23 @@ carry_matrix_kernel(const float* __restrict__ local_states, float* __restrict__ 
       __syncthreads();    // the columns are written; the chunk before has been used
       for (int idx = tid; idx < D * 32; idx += 256) {
         const int d = idx / 32, e = idx % 32;
-        sM[d * 33 + e] = e0 + e < D ? local_states[(row0 + d) * Vx + V + e0 + e] : 0.f;
+        sM[d * 36 + e] = e0 + e < D ? local_states[(row0 + d) * Vx + V + e0 + e] : 0.f;
       }
       __syncthreads();
-      const int ne = min(32, D - e0);
-      for (int e = 0; e < ne; ++e) {
-        const float c = cols[(e0 + e) * kCarryColumns + jj];
+      for (int e = 0; e < 32; e += 4) {          // (columns past D are zeros in sM; the current columns there are read as 0)
+        float c[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) c[i] = e0 + e + i < D ? cols[(e0 + e + i) * kCarryColumns + jj] : 0.f;
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
           const int d = d0 + kCarryRows * k;
-          if (d < D) acc[k] = fmaf(sM[d * 33 + e], c, acc[k]);
+          if (d < D) {
+            const float4 m = *reinterpret_cast<const float4*>(sM + d * 36 + e);
+            acc[k] = fmaf(m.x, c[0], acc[k]);
+            acc[k] = fmaf(m.y, c[1], acc[k]);
+            acc[k] = fmaf(m.z, c[2], acc[k]);
+            acc[k] = fmaf(m.w, c[3], acc[k]);
+          }
         }
       }
     }
@@ -315,7 +322,9 @@ int launch_walk(int mode, int pieces, const void* proj, long long stride, int q_
   const int Vx = V + extra;
   const int BV = Vx <= 8 ? 8 : Vx <= 16 ? 16 : Vx <= 32 ? 32 : kColumns;     // (a block is whole warps: 8 columns x 4 lanes at least)
   const int Dp = padded_rows(D);
-  const int lanes = mode != kWhole || Dp <= 16 ? 4 : Dp <= 32 ? 8 : 16;      // pieces: many blocks an SM, few lanes a column
+  // pieces: many blocks an SM, so four lanes a column (the fewest shuffles and instructions in all; eight lanes with half
+  // the rows each measured slower: 0.88 against 0.71 ms a layer of gated linear attention at keys of 128)
+  const int lanes = mode != kWhole || Dp <= 16 ? 4 : Dp <= 32 ? 8 : 16;
   const int n_arrays = RULE == kRuleDelta ? 5 : 3;
   const int per_token = (n_arrays * Dp + BV) * (int)sizeof(float);
   const int stage = max(1, min(16, kStageBytes / per_token));
@@ -366,13 +375,13 @@ int launch_recurrence(const void* proj, long long stride, int q_col, int k_col, 
   if (RULE == kRuleGla)
     e = launch_plain(carry_diagonal_kernel, dim3(n_seqs, heads, (D * V + 255) / 256), dim3(256), 0, stream,
                      (const float*)local_states, start_states, state, seq_slot, seq_start, cu_new, heads, D, V, pieces);
-  else if ((size_t)D * (kCarryColumns + 33) * sizeof(float) > 48 * 1024 &&
+  else if ((size_t)D * (kCarryColumns + 36) * sizeof(float) > 48 * 1024 &&
            cudaFuncSetAttribute(carry_matrix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)((size_t)D * (kCarryColumns + 33) * sizeof(float))) != cudaSuccess)
+                                (int)((size_t)D * (kCarryColumns + 36) * sizeof(float))) != cudaSuccess)
     return ember_fail("%s (carry): shared memory for a key size of %d", name, D);
   else
     e = launch_plain(carry_matrix_kernel, dim3(n_seqs, heads, (V + kCarryColumns - 1) / kCarryColumns), dim3(256),
-                     (size_t)D * (kCarryColumns + 33) * sizeof(float), stream, (const float*)local_states, start_states, state,
+                     (size_t)D * (kCarryColumns + 36) * sizeof(float), stream, (const float*)local_states, start_states, state,
                      seq_slot, seq_start, cu_new, heads, D, V, pieces);
   if (e != cudaSuccess) return ember_fail("%s (carry): %s", name, cudaGetErrorString(e));
   return launch_walk<T, RULE>(kFromStart, pieces, proj, stride, q_col, k_col, v_col, a_col, a_bias, z, coef, unit_eps, state, out,
