@@ -148,6 +148,40 @@ recurrence_kernel(const T* __restrict__ proj, long long stride, int q_col, int k
       const float4* k4 = reinterpret_cast<const float4*>(ks + i * Dp) + sub;
       const float4* d4 = reinterpret_cast<const float4*>(ds + i * Dp) + sub;
       float o0 = 0.f, o1 = 0.f;
+      if (mode == kLocal) {      // the first walk of pieces wants the states alone: no read-out
+        if (RULE == kRuleGla) {
+#pragma unroll
+          for (int g = 0; g < R / 4; ++g) {
+            const float4 kk = k4[kSub * g], dd = d4[kSub * g];
+            S[4 * g + 0] = fmaf(dd.x, S[4 * g + 0], kk.x * v);
+            S[4 * g + 1] = fmaf(dd.y, S[4 * g + 1], kk.y * v);
+            S[4 * g + 2] = fmaf(dd.z, S[4 * g + 2], kk.z * v);
+            S[4 * g + 3] = fmaf(dd.w, S[4 * g + 3], kk.w * v);
+          }
+        } else {
+          const float4* u4 = reinterpret_cast<const float4*>(us + i * Dp) + sub;
+          const float4* a4 = reinterpret_cast<const float4*>(as + i * Dp) + sub;
+          float p0 = 0.f, p1 = 0.f;
+#pragma unroll
+          for (int g = 0; g < R / 4; ++g) {
+            const float4 uu = u4[kSub * g];
+            p0 = fmaf(uu.x, S[4 * g + 0], p0);
+            p1 = fmaf(uu.y, S[4 * g + 1], p1);
+            p0 = fmaf(uu.z, S[4 * g + 2], p0);
+            p1 = fmaf(uu.w, S[4 * g + 3], p1);
+          }
+          const float uS = sum_of_column<SUB>(p0 + p1);
+#pragma unroll
+          for (int g = 0; g < R / 4; ++g) {
+            const float4 kk = k4[kSub * g], dd = d4[kSub * g], aa = a4[kSub * g];
+            S[4 * g + 0] = fmaf(dd.x, S[4 * g + 0], fmaf(-aa.x, uS, kk.x * v));
+            S[4 * g + 1] = fmaf(dd.y, S[4 * g + 1], fmaf(-aa.y, uS, kk.y * v));
+            S[4 * g + 2] = fmaf(dd.z, S[4 * g + 2], fmaf(-aa.z, uS, kk.z * v));
+            S[4 * g + 3] = fmaf(dd.w, S[4 * g + 3], fmaf(-aa.w, uS, kk.w * v));
+          }
+        }
+        continue;
+      }
       if (RULE == kRuleGla) {
 #pragma unroll
         for (int g = 0; g < R / 4; ++g) {
