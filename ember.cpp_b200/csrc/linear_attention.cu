@@ -272,6 +272,7 @@ carry_diagonal_kernel(const float* __restrict__ local_states, float* __restrict_
 constexpr int kCarryColumns = 16;
 constexpr int kCarryRows = 256 / kCarryColumns;     // rows that the threads cover at once
 
+template <int NK>      // rows a thread: 16 NK covers the key size
 __global__ void __launch_bounds__(256)
 carry_matrix_kernel(const float* __restrict__ local_states, float* __restrict__ start_states, float* __restrict__ state,
                     const int* __restrict__ seq_slot, const int* __restrict__ seq_start, const int* __restrict__ cu_new,
@@ -288,9 +289,9 @@ carry_matrix_kernel(const float* __restrict__ local_states, float* __restrict__ 
   const int n_pieces = (n + kPiece - 1) / kPiece, Vx = V + D;
   float* st = state + (((size_t)slot * heads + h) * D) * V;
   const bool carried = seq_start[s] > 0;
-  float cur[16];                                   // rows d0 + 16 k (key sizes up to 256)
+  float cur[NK];                                   // rows d0 + 16 k
 #pragma unroll
-  for (int k = 0; k < 16; ++k) {
+  for (int k = 0; k < NK; ++k) {
     const int d = d0 + kCarryRows * k;
     cur[k] = (carried && d < D && j < V) ? st[(size_t)d * V + j] : 0.f;
   }
@@ -298,16 +299,16 @@ carry_matrix_kernel(const float* __restrict__ local_states, float* __restrict__ 
     const size_t row0 = (((size_t)s * pieces + p) * heads + h) * D;
     __syncthreads();      // the piece before has read the columns
 #pragma unroll
-    for (int k = 0; k < 16; ++k) {
+    for (int k = 0; k < NK; ++k) {
       const int d = d0 + kCarryRows * k;
       if (d < D) {
         cols[d * kCarryColumns + jj] = cur[k];
         if (j < V) start_states[(row0 + d) * V + j] = cur[k];
       }
     }
-    float acc[16];
+    float acc[NK];
 #pragma unroll
-    for (int k = 0; k < 16; ++k) acc[k] = 0.f;
+    for (int k = 0; k < NK; ++k) acc[k] = 0.f;
     for (int e0 = 0; e0 < D; e0 += 32) {
       __syncthreads();    // the columns are written; the chunk before has been used
       for (int idx = tid; idx < D * 32; idx += 256) {
@@ -320,7 +321,7 @@ carry_matrix_kernel(const float* __restrict__ local_states, float* __restrict__ 
 #pragma unroll
         for (int i = 0; i < 4; ++i) c[i] = e0 + e + i < D ? cols[(e0 + e + i) * kCarryColumns + jj] : 0.f;
 #pragma unroll
-        for (int k = 0; k < 16; ++k) {
+        for (int k = 0; k < NK; ++k) {
           const int d = d0 + kCarryRows * k;
           if (d < D) {
             const float4 m = *reinterpret_cast<const float4*>(sM + d * 36 + e);
@@ -333,13 +334,13 @@ carry_matrix_kernel(const float* __restrict__ local_states, float* __restrict__ 
       }
     }
 #pragma unroll
-    for (int k = 0; k < 16; ++k) {
+    for (int k = 0; k < NK; ++k) {
       const int d = d0 + kCarryRows * k;
       cur[k] = (d < D && j < V) ? acc[k] + local_states[(row0 + d) * Vx + j] : 0.f;
     }
   }
 #pragma unroll
-  for (int k = 0; k < 16; ++k) {
+  for (int k = 0; k < NK; ++k) {
     const int d = d0 + kCarryRows * k;
     if (d < D && j < V) st[(size_t)d * V + j] = cur[k];
   }
@@ -409,14 +410,22 @@ int launch_recurrence(const void* proj, long long stride, int q_col, int k_col, 
   if (RULE == kRuleGla)
     e = launch_plain(carry_diagonal_kernel, dim3(n_seqs, heads, (D * V + 255) / 256), dim3(256), 0, stream,
                      (const float*)local_states, start_states, state, seq_slot, seq_start, cu_new, heads, D, V, pieces);
-  else if ((size_t)D * (kCarryColumns + 36) * sizeof(float) > 48 * 1024 &&
-           cudaFuncSetAttribute(carry_matrix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)((size_t)D * (kCarryColumns + 36) * sizeof(float))) != cudaSuccess)
-    return ember_fail("%s (carry): shared memory for a key size of %d", name, D);
-  else
-    e = launch_plain(carry_matrix_kernel, dim3(n_seqs, heads, (V + kCarryColumns - 1) / kCarryColumns), dim3(256),
-                     (size_t)D * (kCarryColumns + 36) * sizeof(float), stream, (const float*)local_states, start_states, state,
-                     seq_slot, seq_start, cu_new, heads, D, V, pieces);
+  else {
+    const size_t smem = (size_t)D * (kCarryColumns + 36) * sizeof(float);
+    const dim3 grid(n_seqs, heads, (V + kCarryColumns - 1) / kCarryColumns);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(carry_matrix_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return ember_fail("%s (carry): shared memory for a key size of %d", name, D);
+    if (D <= 64)
+      e = launch_plain(carry_matrix_kernel<4>, grid, dim3(256), smem, stream, (const float*)local_states, start_states, state,
+                       seq_slot, seq_start, cu_new, heads, D, V, pieces);
+    else if (D <= 128)
+      e = launch_plain(carry_matrix_kernel<8>, grid, dim3(256), smem, stream, (const float*)local_states, start_states, state,
+                       seq_slot, seq_start, cu_new, heads, D, V, pieces);
+    else
+      e = launch_plain(carry_matrix_kernel<16>, grid, dim3(256), smem, stream, (const float*)local_states, start_states, state,
+                       seq_slot, seq_start, cu_new, heads, D, V, pieces);
+  }
   if (e != cudaSuccess) return ember_fail("%s (carry): %s", name, cudaGetErrorString(e));
   return launch_walk<T, RULE>(kFromStart, pieces, proj, stride, q_col, k_col, v_col, a_col, a_bias, z, coef, unit_eps, state, out,
                               seq_slot, seq_start, cu_new, n_seqs, heads, D, V, local_states, start_states, stream, name);

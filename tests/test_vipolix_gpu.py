@@ -85,7 +85,7 @@ def feed(step_fn, data, dt, stride):
 
 # ------------------------------------------------------------------------------ token shift, the per-layer input
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("width", [60, 320])
+@pytest.mark.parametrize("width", [60, 384])
 def test_token_shift_over_steps(ops, dtype, width):
     dt = DT[dtype]
     data = {s: rnd(s, n, width, scale=2.0).to(dt) for s, n in LENGTHS.items()}
@@ -98,7 +98,7 @@ def test_token_shift_over_steps(ops, dtype, width):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("width, dim, layers", [(64, 8, 3), (60, 5, 2), (320, 48, 1)])
+@pytest.mark.parametrize("width, dim, layers", [(64, 8, 3), (60, 5, 2), (384, 48, 1)])
 def test_the_per_layer_input_from_the_token_ids(ops, dtype, width, dim, layers):
     dt, vocab, T, eps = DT[dtype], 50, 23, 1e-5
     table, gate, proj = rnd(1, vocab, layers * dim).to(dt), rnd(2, dim, width, scale=0.3).to(dt), rnd(3, width, dim, scale=0.3).to(dt)
@@ -352,7 +352,7 @@ def plain_rows(qkv, heads, kv, hd, vd, chunk, scale, temps):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads, kv, hd, vd, chunk", [(8, 2, 64, 64, 44), (6, 3, 96, 96, 64), (6, 3, 24, 40, 33), (2, 1, 64, 64, 130),
+@pytest.mark.parametrize("heads, kv, hd, vd, chunk", [(8, 2, 64, 64, 44), (12, 4, 96, 96, 50), (6, 3, 24, 40, 33), (2, 1, 64, 64, 130),
                                                       (4, 4, 32, 32, 128), (3, 1, 12, 10, 9)])
 def test_attention_inside_chunks_with_a_sink_and_a_factor_a_head(ops, dtype, heads, kv, hd, vd, chunk):
     lengths = (300, 77, 140)
